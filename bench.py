@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the fused convolution forward + VJP (edges/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1|2|3] [--impl ours|reference]
+
+A step is one forward and one backward (dx, dy, ds) of the operator over one
+synthetic graph of the chosen configuration, 128 channels, lmax = 3, float32,
+with the cotangent dm = 2 * out of the loss sum(out^2).  `value` is measured
+with all operands resident in HBM; `e2e` runs the same step through
+`Convolution.__call__` + autograd with the operands in pinned host memory,
+copied to the device inside the timed region, and reads the loss and dx back.
+
+With N > 1 (torchrun) every rank convolves its own graph of the same
+configuration (different seed) — the reference's data-parallel mode over
+independent graphs, which issues no collective — and the job value is the sum
+of the ranks' edges divided by the slowest rank's time.
+
+`--impl reference` times the CPU oracle port of the reference algorithm
+(OpenMP, all host cores) on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "convolution_fwd_vjp_edges_per_s"
+UNIT = "edges/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload_name(config: int) -> str:
+    return {
+        1: "config1: N=4096 open cube, cutoff 4.5 A, x=0e+1o, y=lmax3, out l<=3, C=128, fwd+VJP",
+        2: "config2: N=25000 periodic cube, cutoff 5 A, x=0e+1o+2e+3o, y=lmax3, out l<=3, C=128, fwd+VJP",
+        3: "config3: 1024 molecules of 10-40 atoms, padded to x128, x=0e+1o+2e+3o, C=128, fwd+VJP",
+        0: "config0: N=512 open cube, cutoff 4.5 A, x=0e+1o, C=128, fwd+VJP",
+    }[config]
+
+
+def algorithmic_bytes(E, N, X, Y, Z, S, C):
+    """Compulsory HBM traffic of each kernel (bytes per launch)."""
+    fwd = 4 * E * (S * C + Y + 1) + 4 * N * (X * C + Z * C + 1)
+    bwd_edges = 4 * E * (2 * S * C + 2 * Y + 1) + 4 * N * (X * C + Z * C + 1)
+    bwd_dx = 4 * E + 4 * N * (X * C + 1)  # the per-edge dx messages are scratch, not algorithmic
+    return {"fwd": fwd, "bwd_edges": bwd_edges, "bwd_dx": bwd_dx}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle port, all host threads, bounded sample
+# ---------------------------------------------------------------------------
+CPU_SAMPLE_EDGES = {0: 10**9, 1: 10**9, 2: 100_000, 3: 100_000}  # config 0/1 run in full on the CPU
+
+
+def cpu_sample(config: int, seed: int, target_edges: int):
+    """The sub-graph made of the edges into the first receivers of the workload
+    (about `target_edges` edges), with the operands those edges need."""
+    from e3j_b200 import problems
+    from e3j_b200.convolution import Convolution
+
+    conv = Convolution((problems.X_IRREPS[config], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    g = problems.make_graph(config, seed)
+    ptr = np.concatenate([[0], np.cumsum(np.bincount(g.receiver[g.receiver < g.num_nodes], minlength=g.num_nodes))])
+    rows = int(np.searchsorted(ptr, target_edges))
+    rows = max(1, min(rows, g.num_nodes))
+    e = int(ptr[rows])
+    sub = problems.Graph(g.num_nodes, g.positions, g.sender[:e], g.receiver[:e], g.vectors[:e])
+    inp = problems.make_inputs(sub, config, conv.num_scalars, conv.source[0].dim, 128, seed)
+    return conv, sub, inp, ptr[: rows + 1], rows
+
+
+def time_cpu(config: int, steps: int, warmup: int, seed: int = 0, target_edges: int | None = None):
+    from oracle import c_oracle
+
+    target_edges = target_edges or CPU_SAMPLE_EDGES[config]
+    conv, sub, inp, ptr_rows, rows = cpu_sample(config, seed, target_edges)
+    n, e = sub.num_nodes, sub.sender.shape[0]
+    ptr = np.full(n + 1, e, np.int32)
+    ptr[: rows + 1] = ptr_rows
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    ptr_t, perm_t = c_oracle.transpose_csr(sub.sender, n)
+    cores = len(os.sched_getaffinity(0))
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+
+    def step():
+        out = c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, sub.sender, ptr, conv.target.dim, wide=False)
+        return c_oracle.conv_bwd(val, idx4, inp.x, inp.y, inp.s, 2 * out, sub.sender, ptr, ptr_t, perm_t, wide=False)
+
+    for _ in range(max(1, warmup)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": e / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"edges into the first {rows} receivers ({e} edges) of the workload, {steps} passes",
+            "ms_per_step": dt * 1e3, "edges": e}  # fmt: skip
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    res = time_cpu(args.config, max(1, args.steps), max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.config), "note": "CPU restatement of the reference algorithm "
+                   "(reference JAX CPU path unavailable: jax is not installed)"},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }  # fmt: skip
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, index: int):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)  # fmt: skip
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.file.read().splitlines():
+            f = [c.strip() for c in row.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, f[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}  # fmt: skip
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from e3j_b200 import ops, problems
+    from e3j_b200.convolution import Convolution
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for --impl ours)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg = args.config
+    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    g = problems.make_graph(cfg, seed=rank)
+    x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
+    X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
+    plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
+    graph = conv.prepare_graph(g.num_nodes, torch.as_tensor(g.sender).to(device), torch.as_tensor(g.receiver).to(device))
+    graph.transposed()
+    n, e, e_real = g.num_nodes, int(g.sender.shape[0]), int(g.num_real_edges)
+
+    out = torch.empty((n, Z, C), device=device)
+    dx, dy, ds = torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)
+    need = int(ops._lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, e))
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    ops.conv_fwd_raw(plan, x, y, s, graph, out)
+    dm = (2 * out).contiguous()
+
+    names = ("fwd", "bwd_edges", "bwd_tail", "bwd_dx")
+
+    def step(events=None):
+        marks = []
+
+        def mark():
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
+
+        mark()
+        ops.conv_fwd_raw(plan, x, y, s, graph, out)
+        mark()
+        for ph in (1, 2, 4):
+            ops.conv_bwd_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds), phases=ph)
+            mark()
+        if events is not None:
+            events.append(marks)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    events: list = []
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        step(events)
+    t_stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t_start.elapsed_time(t_stop)
+    per_kernel = {k: 0.0 for k in names}
+    for marks in events:
+        for k, a, b in zip(names, marks[:-1], marks[1:]):
+            per_kernel[k] += a.elapsed_time(b)
+    per_kernel = {k: v / args.steps for k, v in per_kernel.items()}
+
+    # ---- end to end through the public API, operands in pinned host memory ----
+    hx, hy, hs = (t.cpu().pin_memory() for t in (x, y, s))
+    h_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    h_dx = torch.empty(x.shape, dtype=torch.float32).pin_memory()
+    del ds, dy, ws
+    torch.cuda.empty_cache()
+
+    def e2e_step():
+        gx = hx.to(device, non_blocking=True).requires_grad_()
+        gy = hy.to(device, non_blocking=True).requires_grad_()
+        gs = hs.to(device, non_blocking=True).requires_grad_()
+        o = conv(gx, gy, gs, graph)
+        loss = (o * o).sum()
+        loss.backward()
+        h_loss.copy_(loss.detach(), non_blocking=True)
+        h_dx.copy_(gx.grad, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+
+    # ---- reduce over ranks: slowest rank, total edges ----
+    stats = torch.tensor([ms_total, e2e_ms, float(e_real)], device=device, dtype=torch.float64)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, e2e_ms, edges_all = mx[0].item(), mx[1].item(), sm[2].item()
+    else:
+        edges_all = float(e_real)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / args.steps
+    peak, peak_kind = load_peaks()
+    alg = algorithmic_bytes(e_real, g.num_real_nodes or n, X, Y, Z, S, C)
+    dominant = max(("fwd", "bwd_edges", "bwd_dx"), key=lambda k: per_kernel[k])
+    achieved = alg[dominant] / (per_kernel[dominant] * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as fh:
+            traffic = json.load(fh).get(f"config{cfg}", {}).get(dominant)
+    cpu = time_cpu(cfg, steps=10, warmup=1) if world == 1 and not args.no_cpu else None
+    line = {
+        "metric": METRIC, "value": edges_all / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(cfg), "nodes_per_gpu": n, "edges_per_gpu": e_real, "channels": C,
+                   "variant": plan.variant, "parallelism": f"independent graphs x{world}",
+                   "l2": "inputs larger than L2 (s and ds are %.0f MB each)" % (s.numel() * 4 / 1e6)},
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
+                     "algorithmic_bytes_per_launch": alg[dominant],
+                     "kernels_ms": per_kernel,
+                     "whole_step_frac": sum(alg.values()) / (ms_step * 1e-3) / 1e9 / peak},
+        "e2e": {"value": edges_all / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": int((hx.numel() + hy.numel() + hs.numel()) * 4),
+                "d2h_bytes_per_step": int(h_dx.numel() * 4 + 4), "ms_per_step": e2e_ms},
+        "gpu_launches": 4 * args.steps,
+        "clocks": clocks,
+    }  # fmt: skip
+    if cpu is not None:
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,123 @@
+"""Loader and in-tree build of ``libe3j_b200.so`` (the CUDA library behind the C ABI).
+
+The library is built next to this file so that it ships with a source
+snapshot; nothing is installed into site-packages.  Loading fails loudly:
+there is no CPU or eager fallback for the operators of this package.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(_HERE, "csrc")
+LIB_PATH = os.path.join(_HERE, "libe3j_b200.so")
+INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
+
+# fast math stays off: results are held to fp32 tolerances
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]  # fmt: skip
+
+SOURCES = ["e3j_b200.cu"]
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def _sources_mtime() -> float:
+    newest = 0.0
+    for root in (CSRC, INCLUDE):
+        for name in os.listdir(root):
+            if name.endswith((".cu", ".cuh", ".h", ".inc")):
+                newest = max(newest, os.path.getmtime(os.path.join(root, name)))
+    return newest
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library for sm_100a with nvcc (cross-compiles without a GPU)."""
+    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _sources_mtime():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise LibraryMissing("nvcc not found: cannot build libe3j_b200.so")
+    cmd = [nvcc, *NVCC_FLAGS, "-Xptxas", "-v", "-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode:
+        print(res.stdout + res.stderr)
+    if res.returncode:
+        raise RuntimeError("nvcc failed building libe3j_b200.so")
+    with open(os.path.join(_HERE, "ptxas_info.txt"), "w") as fh:
+        fh.write(res.stderr)
+    return LIB_PATH
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    c = ctypes
+    vp, i32, i64 = c.c_void_p, c.c_int32, c.c_int64
+    lib.e3j_b200_last_error.restype = c.c_char_p
+    lib.e3j_b200_last_error.argtypes = []
+    lib.e3j_b200_version.restype = c.c_char_p
+    lib.e3j_b200_version.argtypes = []
+    lib.e3j_b200_get_device_properties.restype = c.c_int
+    lib.e3j_b200_get_device_properties.argtypes = [c.POINTER(i32)]
+    lib.e3j_b200_plan_create.restype = c.c_int
+    lib.e3j_b200_plan_create.argtypes = [vp, i32, i32, i32, i32, i32, i32, i32, i32, c.POINTER(vp)]
+    lib.e3j_b200_plan_destroy.restype = None
+    lib.e3j_b200_plan_destroy.argtypes = [vp]
+    lib.e3j_b200_plan_variant.restype = c.c_int
+    lib.e3j_b200_plan_variant.argtypes = [vp]
+    lib.e3j_b200_conv_fwd.restype = c.c_int
+    lib.e3j_b200_conv_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i64, i32, vp]
+    lib.e3j_b200_conv_bwd_workspace_bytes.restype = c.c_size_t
+    lib.e3j_b200_conv_bwd_workspace_bytes.argtypes = [vp, i32, i64]
+    lib.e3j_b200_conv_bwd.restype = c.c_int
+    lib.e3j_b200_conv_bwd.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp]
+    lib.e3j_b200_conv_bwd_phases.restype = c.c_int
+    lib.e3j_b200_conv_bwd_phases.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp, i32]
+
+
+#: every symbol declared in include/e3j_b200.h
+EXPORTED_SYMBOLS = (
+    "e3j_b200_last_error",
+    "e3j_b200_version",
+    "e3j_b200_get_device_properties",
+    "e3j_b200_plan_create",
+    "e3j_b200_plan_destroy",
+    "e3j_b200_plan_variant",
+    "e3j_b200_conv_fwd",
+    "e3j_b200_conv_bwd_workspace_bytes",
+    "e3j_b200_conv_bwd",
+    "e3j_b200_conv_bwd_phases",
+)
+
+
+def lib() -> ctypes.CDLL:
+    """Return the loaded library; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LibraryMissing(
+                f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(or e3j_b200._lib.build()). There is no fallback path."
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        _declare(handle)
+        _lib = handle
+    return _lib
+
+
+class E3JError(RuntimeError):
+    """Failure reported by the library, message prefixed ``E3J_ERROR[...]``."""
+
+
+def check(code: int) -> None:
+    if code:
+        raise E3JError(lib().e3j_b200_last_error().decode())

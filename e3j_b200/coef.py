@@ -1,0 +1,120 @@
+"""Packed coefficient tables crossing the custom-call boundary.
+
+A table row is the C struct ``{Val val; Idx i, j, k[, l];}`` aligned to the
+next power of two of its size, reinterpreted as a 2-D array of ``Idx`` words
+(8 bytes per row for uint8 indices + float32 values, 32 bytes for int32).
+Byte layout follows src/e3j/ops/coef.py:92-169 and the device structs it is
+checked against (lib/e3j_ops/cuda/convolution.cuh:31-44); transposition for
+the backward tables follows src/e3j/ops/coef.py:171-185.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+import numpy as np
+
+SUPPORTED_VAL_DTYPES = ("float16", "float32", "float64")
+SUPPORTED_IDX_DTYPES = ("int32", "uint8")
+
+
+def next_pow2(n: int) -> int:
+    return 1 << (int(n) - 1).bit_length()
+
+
+def resolve_val_dtype(input_dtype) -> str:
+    name = np.dtype(input_dtype).name
+    if name not in SUPPORTED_VAL_DTYPES:
+        raise TypeError(
+            f"Fused CUDA ops support value dtypes {SUPPORTED_VAL_DTYPES}, got {name!r}. Cast the operands."
+        )
+    return name
+
+
+@dataclass
+class Coef:
+    val: np.ndarray
+    idx: np.ndarray
+    val_dtype: str = "float32"
+    idx_dtype: str = "int32"
+
+    rank: ClassVar[int] = 3
+    index_names: ClassVar[tuple] = ("i", "j", "k")
+
+    def __post_init__(self):
+        self.val_dtype = np.dtype(self.val_dtype).name
+        self.idx_dtype = np.dtype(self.idx_dtype).name
+        if self.val_dtype not in SUPPORTED_VAL_DTYPES:
+            raise ValueError(f"unsupported value dtype {self.val_dtype}")
+        if self.idx_dtype not in SUPPORTED_IDX_DTYPES:
+            raise ValueError(f"unsupported index dtype {self.idx_dtype}")
+        self.val = np.asarray(self.val)
+        self.idx = np.asarray(self.idx)
+        assert self.idx.shape[:-1] == self.val.shape
+        assert self.idx.shape[-1] == self.rank
+
+    @classmethod
+    def struct_dtype(cls, val_t, idx_t) -> np.dtype:
+        val_t, idx_t = np.dtype(val_t), np.dtype(idx_t)
+        fields = [("val", val_t)] + [(n, idx_t) for n in cls.index_names]
+        dt = np.dtype(fields, align=True)
+        target = next_pow2(val_t.itemsize + cls.rank * idx_t.itemsize)
+        if dt.itemsize < target:
+            dt = np.dtype(
+                {
+                    "names": dt.names,
+                    "formats": [dt.fields[n][0] for n in dt.names],
+                    "offsets": [dt.fields[n][1] for n in dt.names],
+                    "itemsize": target,
+                }
+            )
+        return dt
+
+    @property
+    def dtype(self) -> np.dtype:
+        return self.struct_dtype(self.val_dtype, self.idx_dtype)
+
+    def pack_numpy(self) -> np.ndarray:
+        out = np.zeros(self.val.shape[0], dtype=self.dtype)  # zeroed padding bytes
+        out["val"] = self.val.astype(self.val_dtype)
+        for col, name in enumerate(self.index_names):
+            out[name] = self.idx[:, col].astype(self.idx_dtype)
+        return out
+
+    def pack(self) -> np.ndarray:
+        """Opaque ``idx_dtype`` array of shape (nnz, sizeof(row) / sizeof(Idx))."""
+        packed = self.pack_numpy()
+        idx_t = np.dtype(self.idx_dtype)
+        numel, mod = divmod(self.dtype.itemsize, idx_t.itemsize)
+        if mod:
+            raise TypeError(f"Cannot pack dtype pair: {idx_t} does not divide {self.dtype.itemsize}B rows.")
+        return packed.view(idx_t).reshape(-1, numel)
+
+    @classmethod
+    def unpack(cls, data: np.ndarray, val_dtype) -> "Coef":
+        data = np.ascontiguousarray(np.asarray(data))
+        idx_t = data.dtype["i"] if data.dtype.fields is not None else data.dtype
+        val_t = np.dtype(val_dtype)
+        row_t = cls.struct_dtype(val_t, idx_t)
+        rows = data.view(np.uint8).reshape(-1, row_t.itemsize).view(row_t).reshape(-1)
+        idx = np.stack([rows[n] for n in cls.index_names], axis=-1)
+        return cls(rows["val"].copy(), idx, val_dtype=val_t, idx_dtype=idx_t)
+
+    def transpose(self, argnums) -> "Coef":
+        """Reorder index columns; rows stably sorted by the new first column."""
+        cols = self.idx.T
+        sigma = np.argsort(cols[argnums[0]], kind="stable")
+        idx = np.stack([cols[a][sigma] for a in argnums], axis=-1)
+        return self.__class__(self.val[sigma], idx, val_dtype=self.val_dtype, idx_dtype=self.idx_dtype)
+
+    def __iter__(self):
+        return zip(self.val, self.idx)
+
+
+@dataclass
+class Coef4D(Coef):
+    """``{val, i = out row, j = x row, k = y component, l = scalar index}``."""
+
+    rank: ClassVar[int] = 4
+    index_names: ClassVar[tuple] = ("i", "j", "k", "l")

@@ -1,0 +1,234 @@
+// Table-driven convolution kernels: any irreps, any channel count.
+//
+// These are the fall-back for tables that match no unrolled variant.  One
+// thread owns one channel of one receiver; the coefficient table is staged in
+// shared memory; output rows are accumulated in shared memory (or directly in
+// the result row when it would not fit) and written once.  No atomics: each
+// receiver row, edge row and sender row has exactly one writer, and every sum
+// runs in a fixed order.
+//
+// Computes what e3j::convolution::kernel / kernel_bwd compute
+// (lib/e3j_ops/cuda/convolution/fwd.cuh:289-403, bwd.cuh:116-321).
+#pragma once
+
+#include "common.cuh"
+
+namespace e3jb {
+namespace generic {
+
+constexpr int kMaxThreadsX = 128;
+
+struct SmemTable {
+    const float *val;
+    const int4 *idx;
+};
+
+// Copies the table to shared memory when `in_smem`, else points at global memory.
+__device__ __forceinline__ SmemTable stage_table(const DeviceTable &t, bool in_smem, float *&smem) {
+    if (!in_smem) return {t.val, t.idx};
+    int4 *sidx = reinterpret_cast<int4 *>(smem);
+    float *sval = reinterpret_cast<float *>(sidx + t.nnz);
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+    const int nthr = blockDim.x * blockDim.y;
+    for (int n = tid; n < t.nnz; n += nthr) {
+        sidx[n] = t.idx[n];
+        sval[n] = t.val[n];
+    }
+    // keep what follows 16-byte aligned
+    smem = sval + ((t.nnz + 3) / 4) * 4;
+    __syncthreads();
+    return {sval, sidx};
+}
+
+// ---------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_kernel(
+    DeviceTable table, bool table_in_smem, bool acc_in_smem, const float *__restrict__ x,
+    const float *__restrict__ y, const float *__restrict__ s, const int32_t *__restrict__ sender,
+    const int32_t *__restrict__ receiver_ptr, float *__restrict__ out, int32_t N, Dims d) {
+    extern __shared__ __align__(16) float smem_raw[];
+    float *smem = smem_raw;
+    const SmemTable tab = stage_table(table, table_in_smem, smem);
+    const int CT = blockDim.x, tx = threadIdx.x;
+    const int C = d.C;
+
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; r < N;
+         r += (int64_t)gridDim.x * blockDim.y) {
+        const int32_t e0 = receiver_ptr[r], e1 = receiver_ptr[r + 1];
+        for (int c0 = 0; c0 < C; c0 += CT) {
+            const int c = c0 + tx;
+            if (c >= C) continue;  // rows of one receiver never synchronise
+            float *acc;
+            int64_t astride;
+            if (acc_in_smem) {
+                acc = smem + (size_t)threadIdx.y * d.Z * CT + tx;
+                astride = CT;
+            } else {
+                acc = out + (r * d.Z) * C + c;
+                astride = C;
+            }
+            for (int z = 0; z < d.Z; z++) acc[z * astride] = 0.f;
+            for (int32_t e = e0; e < e1; e++) {
+                const int32_t a = sender[e];
+                if (!in_range(a, N)) continue;
+                const float *xa = x + ((int64_t)a * d.X) * C + c;
+                const float *se = s + ((int64_t)e * d.S) * C + c;
+                const float *ye = y + (int64_t)e * d.Y;
+                int cur = -1;
+                float run = 0.f;
+                for (int n = 0; n < table.nnz; n++) {
+                    const int4 id = tab.idx[n];
+                    if (id.x != cur) {
+                        if (cur >= 0) acc[cur * astride] += run;
+                        cur = id.x;
+                        run = 0.f;
+                    }
+                    run = fmaf(tab.val[n] * ye[id.z], xa[(int64_t)id.y * C] * se[(int64_t)id.w * C], run);
+                }
+                if (cur >= 0) acc[cur * astride] += run;
+            }
+            if (acc_in_smem) {
+                float *o = out + (r * d.Z) * C + c;
+                for (int z = 0; z < d.Z; z++) o[(int64_t)z * C] = acc[z * astride];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// backward, pass 1: per receiver, per edge -> ds[e], dy[e] and the edge's dx message
+// ---------------------------------------------------------------------------
+// Shared memory per receiver row: ds[S*CT] | dxm[X*CT] | dy[Y*CT] | warp partials [4*Y].
+__global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
+    DeviceTable table, bool table_in_smem, const float *__restrict__ x, const float *__restrict__ y,
+    const float *__restrict__ s, const float *__restrict__ dm, const int32_t *__restrict__ sender,
+    const int32_t *__restrict__ receiver_ptr, float *__restrict__ dxm, float *__restrict__ dy,
+    float *__restrict__ ds, int32_t N, Dims d) {
+    extern __shared__ __align__(16) float smem_raw[];
+    float *smem = smem_raw;
+    const SmemTable tab = stage_table(table, table_in_smem, smem);
+    const int CT = blockDim.x, tx = threadIdx.x, C = d.C;
+    const int per_row = (d.S + d.X + d.Y) * CT + 4 * d.Y;
+    float *ds_acc = smem + (size_t)threadIdx.y * per_row;
+    float *dx_acc = ds_acc + d.S * CT;
+    float *dy_acc = dx_acc + d.X * CT;
+    float *dy_warp = dy_acc + d.Y * CT;
+    const bool one_warp = (CT == 32);  // blockDim.y > 1 only in this case
+    const int lane = tx & 31, warp = tx >> 5, nwarp = CT >> 5;
+
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; r < N;
+         r += (int64_t)gridDim.x * blockDim.y) {
+        const int32_t e0 = receiver_ptr[r], e1 = receiver_ptr[r + 1];
+        const float *g = dm + (r * d.Z) * C;
+        for (int32_t e = e0; e < e1; e++) {
+            const int32_t a = sender[e];
+            const bool valid = in_range(a, N);
+            for (int k = 0; k < d.Y; k++) dy_acc[k * CT + tx] = 0.f;
+            for (int c0 = 0; c0 < C; c0 += CT) {
+                const int c = c0 + tx;
+                const bool act = c < C;
+                for (int l = 0; l < d.S; l++) ds_acc[l * CT + tx] = 0.f;
+                for (int j = 0; j < d.X; j++) dx_acc[j * CT + tx] = 0.f;
+                if (valid && act) {
+                    const float *xa = x + ((int64_t)a * d.X) * C + c;
+                    const float *se = s + ((int64_t)e * d.S) * C + c;
+                    const float *ye = y + (int64_t)e * d.Y;
+                    for (int n = 0; n < table.nnz; n++) {
+                        const int4 id = tab.idx[n];
+                        const float t = tab.val[n] * g[(int64_t)id.x * C + c];
+                        const float xv = xa[(int64_t)id.y * C];
+                        const float yv = ye[id.z];
+                        const float sv = se[(int64_t)id.w * C];
+                        ds_acc[id.w * CT + tx] = fmaf(t * yv, xv, ds_acc[id.w * CT + tx]);
+                        dx_acc[id.y * CT + tx] = fmaf(t * yv, sv, dx_acc[id.y * CT + tx]);
+                        dy_acc[id.z * CT + tx] = fmaf(t * sv, xv, dy_acc[id.z * CT + tx]);
+                    }
+                }
+                if (act) {
+                    float *dse = ds + ((int64_t)e * d.S) * C + c;
+                    for (int l = 0; l < d.S; l++) dse[(int64_t)l * C] = ds_acc[l * CT + tx];
+                    float *dxe = dxm + ((int64_t)e * d.X) * C + c;
+                    for (int j = 0; j < d.X; j++) dxe[(int64_t)j * C] = dx_acc[j * CT + tx];
+                }
+            }
+            // channel reduction of dy: xor-butterfly inside each warp, then warps in order
+            for (int k = 0; k < d.Y; k++) {
+                float v = dy_acc[k * CT + tx];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) dy_warp[warp * d.Y + k] = v;
+            }
+            if (one_warp) __syncwarp(); else __syncthreads();
+            for (int k = tx; k < d.Y; k += CT) {
+                float v = 0.f;
+                for (int w = 0; w < nwarp; w++) v += dy_warp[w * d.Y + k];
+                dy[(int64_t)e * d.Y + k] = v;
+            }
+            if (one_warp) __syncwarp(); else __syncthreads();
+        }
+    }
+}
+
+// Edges at or beyond receiver_ptr[N] belong to no receiver: exact zeros
+// (lib/e3j_ops/cuda/convolution/bwd.cuh:308-319).
+__global__ void zero_tail_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t E,
+                                 float *__restrict__ dxm, int64_t dxm_row, float *__restrict__ dy,
+                                 int64_t dy_row, float *__restrict__ ds, int64_t ds_row) {
+    const int64_t first = receiver_ptr[N];
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (first >= E) return;
+    for (int64_t t = first * dxm_row + tid; t < E * dxm_row; t += step) dxm[t] = 0.f;
+    for (int64_t t = first * dy_row + tid; t < E * dy_row; t += step) dy[t] = 0.f;
+    for (int64_t t = first * ds_row + tid; t < E * ds_row; t += step) ds[t] = 0.f;
+}
+
+// ---------------------------------------------------------------------------
+// backward, pass 2: dx[a] = sum over the sender segment of the edges' dx messages,
+// in sender-sorted order.  One block per sender row; rows of XC floats.
+// ---------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(256) dx_reduce_kernel(const float *__restrict__ dxm,
+                                                        const int32_t *__restrict__ sender_ptr_t,
+                                                        const int32_t *__restrict__ perm_t,
+                                                        float *__restrict__ dx, int32_t N,
+                                                        int64_t XC) {
+    using V = typename std::conditional<VEC == 4, float4, float>::type;
+    const int64_t nvec = XC / VEC;
+    for (int64_t a = blockIdx.x; a < N; a += gridDim.x) {
+        const int32_t p0 = sender_ptr_t[a], p1 = sender_ptr_t[a + 1];
+        for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float acc[VEC];
+#pragma unroll
+            for (int q = 0; q < VEC; q++) acc[q] = 0.f;
+            int32_t p = p0;
+            for (; p + 4 <= p1; p += 4) {
+                V t[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    t[u] = reinterpret_cast<const V *>(dxm + (int64_t)perm_t[p + u] * XC)[v];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float *f = reinterpret_cast<const float *>(&t[u]);
+#pragma unroll
+                    for (int q = 0; q < VEC; q++) acc[q] += f[q];
+                }
+            }
+            for (; p < p1; p++) {
+                V t = reinterpret_cast<const V *>(dxm + (int64_t)perm_t[p] * XC)[v];
+                const float *f = reinterpret_cast<const float *>(&t);
+#pragma unroll
+                for (int q = 0; q < VEC; q++) acc[q] += f[q];
+            }
+            V o;
+            float *of = reinterpret_cast<float *>(&o);
+#pragma unroll
+            for (int q = 0; q < VEC; q++) of[q] = acc[q];
+            reinterpret_cast<V *>(dx + a * XC)[v] = o;
+        }
+    }
+}
+
+}  // namespace generic
+}  // namespace e3jb

@@ -1,0 +1,312 @@
+// C ABI of the e3j_b200 library: plans, launchers, error reporting.
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include "common.cuh"
+#include "conv_generic.cuh"
+#include "conv_unrolled.cuh"
+
+namespace e3jb {
+
+static thread_local std::string g_last_error;
+
+int set_error(int code, const std::string &msg) {
+    static const char *kPrefix[] = {"",
+                                    "E3J_ERROR[Internal]: ",
+                                    "E3J_ERROR[InvalidArgument]: ",
+                                    "E3J_ERROR[CudaLaunch]: ",
+                                    "E3J_ERROR[CudaRuntime]: ",
+                                    "E3J_ERROR[Unimplemented]: "};
+    g_last_error = std::string(code >= 1 && code <= 5 ? kPrefix[code] : "E3J_ERROR: ") + msg;
+    return code;
+}
+
+int check_launch(const char *what, int debug, cudaStream_t stream) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return set_error(E3J_B200_CUDA_LAUNCH, std::string(what) + ": " + cudaGetErrorString(e));
+    if (debug > 0) {
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess)
+            return set_error(E3J_B200_CUDA_RUNTIME, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    return E3J_B200_OK;
+}
+
+struct DeviceLimits {
+    int device = -1;
+    int sm_count = 0;
+    int smem_optin = 0;
+};
+
+static int current_limits(DeviceLimits &lim) {
+    E3JB_CUDA_TRY(cudaGetDevice(&lim.device));
+    E3JB_CUDA_TRY(cudaDeviceGetAttribute(&lim.sm_count, cudaDevAttrMultiProcessorCount, lim.device));
+    E3JB_CUDA_TRY(
+        cudaDeviceGetAttribute(&lim.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, lim.device));
+    return E3J_B200_OK;
+}
+
+}  // namespace e3jb
+
+using namespace e3jb;
+
+struct e3j_b200_plan {
+    Dims d{};
+    int32_t nnz = 0;
+    int variant = E3J_B200_VARIANT_GENERIC;
+    DeviceLimits lim;
+    std::vector<TableRow> rows;  // host copy, table order
+    float *d_val = nullptr;
+    int4 *d_idx = nullptr;
+    unrolled::DevicePlan un{};  // per-variant device tables (null when generic)
+};
+
+extern "C" {
+
+const char *e3j_b200_last_error(void) { return g_last_error.c_str(); }
+
+const char *e3j_b200_version(void) { return "e3j_b200 0.1.0 sm_100a"; }
+
+int e3j_b200_get_device_properties(int32_t out[7]) {
+    if (!out) return set_error(E3J_B200_INVALID_ARGUMENT, "out is null");
+    int dev = 0, v = 0;
+    E3JB_CUDA_TRY(cudaGetDevice(&dev));
+    out[0] = dev;
+    const cudaDeviceAttr attrs[6] = {cudaDevAttrMaxSharedMemoryPerBlock,
+                                     cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                     cudaDevAttrMaxSharedMemoryPerMultiprocessor,
+                                     cudaDevAttrMaxThreadsPerMultiProcessor,
+                                     cudaDevAttrMaxBlocksPerMultiprocessor,
+                                     cudaDevAttrMaxRegistersPerMultiprocessor};
+    for (int i = 0; i < 6; i++) {
+        E3JB_CUDA_TRY(cudaDeviceGetAttribute(&v, attrs[i], dev));
+        out[i + 1] = v;
+    }
+    return E3J_B200_OK;
+}
+
+int e3j_b200_plan_create(const void *coef_host, int32_t nnz, int32_t idx_bytes, int32_t X,
+                         int32_t Y, int32_t Z, int32_t S, int32_t C, int32_t force_generic,
+                         e3j_b200_plan **plan_out) {
+    if (!plan_out) return set_error(E3J_B200_INVALID_ARGUMENT, "plan is null");
+    *plan_out = nullptr;
+    if (nnz < 0 || (nnz > 0 && !coef_host))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "coefficient table is null");
+    if (idx_bytes != 1 && idx_bytes != 4)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "unsupported (IDX, VAL) dtype pair");
+    if (X <= 0 || Y <= 0 || Z <= 0 || S <= 0 || C <= 0)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "dimensions must be positive");
+
+    auto *p = new e3j_b200_plan();
+    p->d = Dims{X, Y, Z, S, C};
+    p->nnz = nnz;
+    p->rows.resize(nnz);
+    const size_t row_bytes = idx_bytes == 1 ? 8 : 32;  // next_pow2(4 + 4 * idx_bytes)
+    const auto *bytes = static_cast<const unsigned char *>(coef_host);
+    for (int32_t n = 0; n < nnz; n++) {
+        const unsigned char *r = bytes + n * row_bytes;
+        TableRow t;
+        std::memcpy(&t.val, r, 4);
+        if (idx_bytes == 1) {
+            t.i = r[4]; t.j = r[5]; t.k = r[6]; t.l = r[7];
+        } else {
+            int32_t q[4];
+            std::memcpy(q, r + 4, 16);
+            t.i = q[0]; t.j = q[1]; t.k = q[2]; t.l = q[3];
+        }
+        if (t.i < 0 || t.i >= Z || t.j < 0 || t.j >= X || t.k < 0 || t.k >= Y || t.l < 0 ||
+            t.l >= S) {
+            delete p;
+            return set_error(E3J_B200_INVALID_ARGUMENT,
+                             "coefficient row " + std::to_string(n) + " indexes out of bounds");
+        }
+        p->rows[n] = t;
+    }
+    int rc = current_limits(p->lim);
+    if (rc) { delete p; return rc; }
+
+    std::vector<float> val(std::max(nnz, 1));
+    std::vector<int4> idx(std::max(nnz, 1));
+    for (int32_t n = 0; n < nnz; n++) {
+        val[n] = p->rows[n].val;
+        idx[n] = make_int4(p->rows[n].i, p->rows[n].j, p->rows[n].k, p->rows[n].l);
+    }
+    auto fail = [&](cudaError_t e, const char *what) {
+        e3j_b200_plan_destroy(p);
+        return set_error(E3J_B200_CUDA_RUNTIME, std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    cudaError_t e;
+    if ((e = cudaMalloc(&p->d_val, val.size() * sizeof(float))) != cudaSuccess) return fail(e, "cudaMalloc");
+    if ((e = cudaMalloc(&p->d_idx, idx.size() * sizeof(int4))) != cudaSuccess) return fail(e, "cudaMalloc");
+    if ((e = cudaMemcpy(p->d_val, val.data(), val.size() * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess)
+        return fail(e, "cudaMemcpy");
+    if ((e = cudaMemcpy(p->d_idx, idx.data(), idx.size() * sizeof(int4), cudaMemcpyHostToDevice)) != cudaSuccess)
+        return fail(e, "cudaMemcpy");
+
+    if (!force_generic) {
+        rc = unrolled::resolve(p->rows, p->d, p->un, p->variant);
+        if (rc) { e3j_b200_plan_destroy(p); return rc; }
+    }
+    *plan_out = p;
+    return E3J_B200_OK;
+}
+
+void e3j_b200_plan_destroy(e3j_b200_plan *p) {
+    if (!p) return;
+    if (p->d_val) cudaFree(p->d_val);
+    if (p->d_idx) cudaFree(p->d_idx);
+    unrolled::release(p->un);
+    delete p;
+}
+
+int e3j_b200_plan_variant(const e3j_b200_plan *p) { return p ? p->variant : -1; }
+
+// ---------------------------------------------------------------------------
+// generic launch geometry
+// ---------------------------------------------------------------------------
+namespace {
+
+struct GenericGeometry {
+    dim3 block;
+    bool table_in_smem;
+    size_t table_bytes;
+};
+
+GenericGeometry generic_geometry(const e3j_b200_plan *p) {
+    GenericGeometry g;
+    const int ct = std::min(generic::kMaxThreadsX, ((p->d.C + 31) / 32) * 32);
+    g.block = dim3(ct, ct == 32 ? 4 : 1, 1);
+    const size_t tb = (size_t)p->nnz * sizeof(int4) + (size_t)((p->nnz + 3) / 4) * 4 * sizeof(float);
+    g.table_in_smem = tb <= 48 * 1024;
+    g.table_bytes = g.table_in_smem ? tb : 0;
+    return g;
+}
+
+int check_common(const e3j_b200_plan *p, int32_t N, int64_t E) {
+    if (!p) return set_error(E3J_B200_INVALID_ARGUMENT, "plan is null");
+    if (N < 0 || E < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative graph size");
+    if (E > 0x7fffffffLL)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "edge count exceeds the int32 CSR offsets");
+    int dev = -1;
+    E3JB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != p->lim.device)
+        return set_error(E3J_B200_INVALID_ARGUMENT,
+                         "plan was created on device " + std::to_string(p->lim.device) +
+                             " but device " + std::to_string(dev) + " is current");
+    return E3J_B200_OK;
+}
+
+}  // namespace
+
+int e3j_b200_conv_fwd(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                      const int32_t *sender, const int32_t *receiver_ptr, float *out, int32_t N,
+                      int64_t E, int32_t debug, e3j_b200_stream stream) {
+    int rc = check_common(p, N, E);
+    if (rc) return rc;
+    if (N == 0) return E3J_B200_OK;
+    if (!x || !out || !receiver_ptr || (E > 0 && (!y || !s || !sender)))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+
+    if (p->variant != E3J_B200_VARIANT_GENERIC)
+        return unrolled::launch_fwd(p->variant, p->un, p->lim.sm_count, x, y, s, sender,
+                                    receiver_ptr, out, N, E, debug, stream);
+
+    const GenericGeometry g = generic_geometry(p);
+    const size_t acc_bytes = (size_t)g.block.y * p->d.Z * g.block.x * sizeof(float);
+    const bool acc_in_smem = g.table_bytes + acc_bytes <= (size_t)p->lim.smem_optin;
+    const size_t smem = g.table_bytes + (acc_in_smem ? acc_bytes : 0);
+    if (smem > 48 * 1024)
+        E3JB_CUDA_TRY(cudaFuncSetAttribute(generic::conv_fwd_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int64_t want = ceil_div64(N, g.block.y);
+    const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
+    DeviceTable t{p->d_val, p->d_idx, p->nnz};
+    generic::conv_fwd_kernel<<<grid, g.block, smem, stream>>>(t, g.table_in_smem, acc_in_smem, x, y,
+                                                              s, sender, receiver_ptr, out, N, p->d);
+    return check_launch("convolution", debug, stream);
+}
+
+size_t e3j_b200_conv_bwd_workspace_bytes(const e3j_b200_plan *p, int32_t N, int64_t E) {
+    (void)N;
+    if (!p || E <= 0) return 256;
+    return ((size_t)E * p->d.X * p->d.C * sizeof(float) + 255) / 256 * 256;
+}
+
+int e3j_b200_conv_bwd(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                      const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                      const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                      float *ds, void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
+                      int32_t debug, e3j_b200_stream stream) {
+    return e3j_b200_conv_bwd_phases(p, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx,
+                                    dy, ds, workspace, workspace_bytes, N, E, debug, stream,
+                                    E3J_B200_BWD_ALL);
+}
+
+int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float *y,
+                             const float *s, const float *dm, const int32_t *sender,
+                             const int32_t *receiver_ptr, const int32_t *sender_ptr_t,
+                             const int32_t *perm_t, float *dx, float *dy, float *ds,
+                             void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
+                             int32_t debug, e3j_b200_stream stream, int32_t phases) {
+    int rc = check_common(p, N, E);
+    if (rc) return rc;
+    if (N == 0) return E3J_B200_OK;
+    if (!x || !dm || !dx || !receiver_ptr || !sender_ptr_t ||
+        (E > 0 && (!y || !s || !sender || !perm_t || !dy || !ds)))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    if (workspace_bytes < e3j_b200_conv_bwd_workspace_bytes(p, N, E) || !workspace)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "workspace is too small");
+    if (reinterpret_cast<uintptr_t>(workspace) % 256)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+    float *dxm = static_cast<float *>(workspace);
+    const Dims &d = p->d;
+
+    if (E > 0 && (phases & E3J_B200_BWD_EDGES)) {
+        if (p->variant != E3J_B200_VARIANT_GENERIC) {
+            rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y, s, dm, sender,
+                                            receiver_ptr, dxm, dy, ds, N, E, debug, stream);
+            if (rc) return rc;
+        } else {
+            const GenericGeometry g = generic_geometry(p);
+            const size_t per_row = ((size_t)(d.S + d.X + d.Y) * g.block.x + 4 * d.Y) * sizeof(float);
+            const size_t smem = g.table_bytes + per_row * g.block.y;
+            if (smem > (size_t)p->lim.smem_optin)
+                return set_error(E3J_B200_UNIMPLEMENTED,
+                                 "irreps too large for the table-driven backward kernel");
+            if (smem > 48 * 1024)
+                E3JB_CUDA_TRY(cudaFuncSetAttribute(generic::conv_bwd_edges_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)smem));
+            const int64_t want = ceil_div64(N, g.block.y);
+            const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
+            DeviceTable t{p->d_val, p->d_idx, p->nnz};
+            generic::conv_bwd_edges_kernel<<<grid, g.block, smem, stream>>>(
+                t, g.table_in_smem, x, y, s, dm, sender, receiver_ptr, dxm, dy, ds, N, d);
+            rc = check_launch("convolution_bwd (edges)", debug, stream);
+            if (rc) return rc;
+        }
+    }
+    if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
+        generic::zero_tail_kernel<<<p->lim.sm_count, 256, 0, stream>>>(
+            receiver_ptr, N, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C);
+        rc = check_launch("convolution_bwd (tail)", debug, stream);
+        if (rc) return rc;
+    }
+    if (!(phases & E3J_B200_BWD_DX)) return E3J_B200_OK;
+    const int64_t XC = (int64_t)d.X * d.C;
+    const int grid = (int)std::min<int64_t>(N, (int64_t)p->lim.sm_count * 16);
+    const bool vec4 = XC % 4 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
+    const int threads = (int)std::min<int64_t>(256, std::max<int64_t>(32, (XC / (vec4 ? 4 : 1) + 31) / 32 * 32));
+    if (vec4)
+        generic::dx_reduce_kernel<4><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, N, XC);
+    else
+        generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, N, XC);
+    return check_launch("convolution_bwd (dx)", debug, stream);
+}
+
+}  // extern "C"

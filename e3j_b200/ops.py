@@ -1,0 +1,321 @@
+"""``convolution`` / ``convolution_bwd`` primitives bound to the CUDA library.
+
+Host-side mirror of src/e3j/ops/convolution.py for torch tensors: same
+argument order and meaning, same checks and error behaviour, the same
+custom-VJP structure (forward -> ``convolution_bwd``; the backward of
+``convolution_bwd`` is three forwards plus three backwards, :526-564), so
+derivatives of any order work.  The reference lowers to
+``jax.ffi.ffi_call("convolution" | "convolution_bwd")`` (:229-242, :433-452);
+here the same operands go through the C ABI of ``libe3j_b200.so`` on the
+current torch CUDA stream.
+
+There is no CPU implementation in this package: tensors must live on a CUDA
+device and the library must be built, otherwise the call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from .coef import Coef4D
+from .graph import GraphCSR, receiver_ptr_from_sorted
+
+GRAPH_ORDERINGS = ("RECEIVER", "SENDER", "NONE")
+
+
+def is_pow2(n: int) -> bool:
+    return n > 0 and (n & (n - 1)) == 0
+
+
+@dataclass
+class CUDAConvolutionParams:
+    num_out: int
+    num_scalars: int
+
+
+# ---------------------------------------------------------------------------
+# plans: one per (table bytes, dims, device)
+# ---------------------------------------------------------------------------
+class ConvPlan:
+    """Owner of one ``e3j_b200_plan``."""
+
+    def __init__(self, coef_packed: np.ndarray, dims: tuple[int, int, int, int, int], force_generic=False):
+        coef_packed = np.ascontiguousarray(coef_packed)
+        if coef_packed.dtype not in (np.dtype(np.uint8), np.dtype(np.int32)):
+            raise TypeError("unsupported (IDX, VAL) dtype pair")
+        idx_bytes = coef_packed.dtype.itemsize
+        if coef_packed.ndim != 2 or coef_packed.shape[1] * idx_bytes != (8 if idx_bytes == 1 else 32):
+            raise ValueError(f"packed Coef4D<{coef_packed.dtype}, float32> expected, got shape {coef_packed.shape}")
+        self.dims = tuple(int(v) for v in dims)
+        self.nnz = int(coef_packed.shape[0])
+        handle = ctypes.c_void_p()
+        _lib.check(
+            _lib.lib().e3j_b200_plan_create(
+                coef_packed.ctypes.data_as(ctypes.c_void_p), self.nnz, idx_bytes, *self.dims,
+                int(bool(force_generic)), ctypes.byref(handle),
+            )
+        )  # fmt: skip
+        self.handle = handle
+        self.device = torch.cuda.current_device()
+
+    @property
+    def variant(self) -> int:
+        return int(_lib.lib().e3j_b200_plan_variant(self.handle))
+
+    def __del__(self):
+        try:
+            if getattr(self, "handle", None):
+                _lib.lib().e3j_b200_plan_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+_plans: dict = {}
+_plans_lock = threading.Lock()
+
+
+def get_plan(coef_packed: np.ndarray, dims, device: torch.device, force_generic: bool = False) -> ConvPlan:
+    coef_packed = np.ascontiguousarray(coef_packed)
+    key = (coef_packed.tobytes(), str(coef_packed.dtype), tuple(dims), device.index, bool(force_generic))
+    with _plans_lock:
+        plan = _plans.get(key)
+        if plan is None:
+            with torch.cuda.device(device):
+                plan = ConvPlan(coef_packed, dims, force_generic)
+            _plans[key] = plan
+        return plan
+
+
+# ---------------------------------------------------------------------------
+# graphs: CSR views the kernels consume
+# ---------------------------------------------------------------------------
+@dataclass
+class ConvGraph:
+    """Receiver-sorted edge list with its CSR offsets and, on demand, the
+    sender-sorted view of ``GraphCSR.transpose`` (src/e3j/data/graph.py:59-72)."""
+
+    num_nodes: int
+    sender: torch.Tensor  # int32 [E]
+    receiver: torch.Tensor  # int32 [E] (sorted; padding = out of range, at the tail)
+    receiver_ptr: torch.Tensor  # int32 [N + 1]
+    sender_ptr_t: torch.Tensor | None = None
+    perm_t: torch.Tensor | None = None
+
+    @classmethod
+    def build(cls, num_nodes: int, sender: torch.Tensor, receiver: torch.Tensor) -> "ConvGraph":
+        sender = sender.to(torch.int32).contiguous()
+        receiver = receiver.to(torch.int32).contiguous()
+        return cls(int(num_nodes), sender, receiver, receiver_ptr_from_sorted(num_nodes, receiver))
+
+    def transposed(self):
+        if self.perm_t is None:
+            perm, graph_t, _ = GraphCSR(self.num_nodes, self.sender, self.receiver).transpose()
+            self.perm_t = perm.contiguous()
+            self.sender_ptr_t = graph_t.receiver_ptr.contiguous()
+        return self.sender_ptr_t, self.perm_t
+
+
+def _wrap_global_index(index: torch.Tensor, num_nodes: int) -> torch.Tensor:
+    """Reduce indices modulo ``num_nodes`` keeping the padding sentinel out of
+    range (src/e3j/ops/convolution.py:39-51)."""
+    from .graph import DUMMY_INDEX
+
+    idx = index.to(torch.int64)
+    return torch.where(idx == DUMMY_INDEX, idx, idx % num_nodes).to(torch.int32)
+
+
+def _ptr(t: torch.Tensor | None):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else ctypes.c_void_p(0)
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device.type != "cuda":
+            raise RuntimeError(
+                "e3j_b200 operators run on CUDA devices only (tensor on "
+                f"{t.device}); there is no CPU path in this package."
+            )
+        if t.device != dev:
+            raise RuntimeError("all operands must live on the same device")
+    return dev
+
+
+DEBUG_LEVEL = 0  # plays e3j.config().debug_level (src/e3j/ops/convolution.py:241)
+
+
+def conv_fwd_raw(plan: ConvPlan, x, y, s, graph: ConvGraph, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One forward launch.  Operands must be float32, contiguous, on one device."""
+    dev = _require_cuda(x, y, s, graph.sender, graph.receiver_ptr)
+    X, Y, Z, S, C = plan.dims
+    n = x.shape[0]
+    if out is None:
+        out = torch.empty((n, Z, C), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(
+            _lib.lib().e3j_b200_conv_fwd(
+                plan.handle, _ptr(x), _ptr(y), _ptr(s), _ptr(graph.sender), _ptr(graph.receiver_ptr),
+                _ptr(out), n, int(y.shape[0]), DEBUG_LEVEL, _stream(),
+            )
+        )  # fmt: skip
+    return out
+
+
+def conv_bwd_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch.Tensor | None = None,
+                 out=None, phases: int = 7):
+    """One backward call.  ``out`` may hold preallocated ``(dx, dy, ds)``; ``phases``
+    selects passes as in ``e3j_b200_conv_bwd_phases``."""
+    dev = _require_cuda(x, y, s, dm, graph.sender, graph.receiver_ptr)
+    n, e = x.shape[0], int(y.shape[0])
+    sender_ptr_t, perm_t = graph.transposed()
+    need = int(_lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, e))
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    dx, dy, ds = out if out is not None else (torch.empty_like(x), torch.empty_like(y), torch.empty_like(s))
+    with torch.cuda.device(dev):
+        _lib.check(
+            _lib.lib().e3j_b200_conv_bwd_phases(
+                plan.handle, _ptr(x), _ptr(y), _ptr(s), _ptr(dm), _ptr(graph.sender), _ptr(graph.receiver_ptr),
+                _ptr(sender_ptr_t), _ptr(perm_t), _ptr(dx), _ptr(dy), _ptr(ds), _ptr(workspace),
+                workspace.numel() * workspace.element_size(), n, e, DEBUG_LEVEL, _stream(), int(phases),
+            )
+        )  # fmt: skip
+    return dx, dy, ds
+
+
+# ---------------------------------------------------------------------------
+# differentiable primitives
+# ---------------------------------------------------------------------------
+class _ConvFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, s, plan, graph):
+        ctx.plan, ctx.graph = plan, graph
+        ctx.save_for_backward(x, y, s)
+        return conv_fwd_raw(plan, x, y, s, graph)
+
+    @staticmethod
+    def backward(ctx, dm):
+        x, y, s = ctx.saved_tensors
+        dx, dy, ds = _ConvBwdFn.apply(x, y, s, dm.contiguous(), ctx.plan, ctx.graph)
+        return dx, dy, ds, None, None
+
+
+class _ConvBwdFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, s, dm, plan, graph):
+        ctx.plan, ctx.graph = plan, graph
+        ctx.save_for_backward(x, y, s, dm)
+        return conv_bwd_raw(plan, x, y, s, dm, graph)
+
+    @staticmethod
+    def backward(ctx, ddx, ddy, dds):
+        # (Dx, Dy, Ds, Ddm) from (Ddx, Ddy, Dds): src/e3j/ops/convolution.py:535-562
+        x, y, s, dm = ctx.saved_tensors
+        plan, graph = ctx.plan, ctx.graph
+        z = torch.zeros_like
+        ddx = z(x) if ddx is None else ddx.contiguous()
+        ddy = z(y) if ddy is None else ddy.contiguous()
+        dds = z(s) if dds is None else dds.contiguous()
+
+        def conv(a, b, c):
+            return _ConvFn.apply(a, b, c, plan, graph)
+
+        def conv_bwd(a, b, c):
+            return _ConvBwdFn.apply(a, b, c, dm, plan, graph)
+
+        ddm = conv(ddx, y, s) + conv(x, ddy, s) + conv(x, y, dds)
+        _, dx_y, dx_s = conv_bwd(ddx, y, s)
+        dy_x, _, dy_s = conv_bwd(x, ddy, s)
+        ds_x, ds_y, _ = conv_bwd(x, y, dds)
+        return dy_x + ds_x, dx_y + ds_y, dx_s + dy_s, ddm, None, None
+
+
+def _check_operands(coef, x, y, s):
+    if isinstance(coef, torch.Tensor):
+        raise TypeError("`coef` must be concrete: it is read at trace time.")
+    if x.ndim != 3:
+        raise NotImplementedError("node features must have shape (num_nodes, num_x, channels)")
+    if y.ndim == x.ndim and y.shape[-1] != 1:
+        raise NotImplementedError("RHS y should have only one channel.")
+    if not is_pow2(int(x.shape[-1])):
+        raise NotImplementedError("LHS x should have power of 2 number of channels.")
+    for t in (x, y, s):
+        if t.dtype != torch.float32:
+            raise _lib.E3JError(
+                "E3J_ERROR[Unimplemented]: the B200 kernels compute in float32; "
+                f"got {t.dtype}. Cast the operands."
+            )
+
+
+def _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic=False):
+    _check_operands(coef, x, y, s)
+    ordering = str(graph_ordering).upper().split(".")[-1]
+    if ordering not in GRAPH_ORDERINGS:
+        raise ValueError(f"unknown graph ordering {graph_ordering!r}")
+    if ordering != "RECEIVER":
+        raise NotImplementedError("the B200 convolution supports RECEIVER graph ordering only.")
+    if y.ndim == 3:
+        y = y[..., 0]
+    dev = _require_cuda(x, y, s)
+    dims = (int(x.shape[1]), int(y.shape[1]), int(params.num_out), int(params.num_scalars), int(x.shape[2]))
+    if s.shape[1] != dims[3] or s.shape[2] != dims[4] or s.shape[0] != y.shape[0]:
+        raise ValueError(f"edge scalars of shape {tuple(s.shape)} do not match (E, {dims[3]}, {dims[4]})")
+    plan = get_plan(np.asarray(coef), dims, dev, force_generic)
+    if isinstance(sender, ConvGraph):
+        graph = sender
+    else:
+        n = int(x.shape[0])
+        graph = ConvGraph.build(n, _wrap_global_index(sender.to(dev), n), _wrap_global_index(receiver.to(dev), n))
+    return plan, graph, x.contiguous(), y.contiguous(), s.contiguous()
+
+
+def convolution(coef, x, y, s, sender, receiver, params, graph_ordering="RECEIVER", y_parity=None,
+                *, force_generic: bool = False) -> torch.Tensor:  # fmt: skip
+    """Fused gather -> CG product -> scalar mixing -> segment sum.
+
+    Args mirror ``e3j.ops.convolution.convolution`` (src/e3j/ops/convolution.py:106-158):
+    ``coef`` packed Coef4D table (numpy, concrete), ``x`` (N, X, C), ``y`` (E, Y),
+    ``s`` (E, S, C), ``sender`` / ``receiver`` (E,) sorted by receiver (``sender``
+    may also be a prepared :class:`ConvGraph`), ``params`` with ``num_out`` and
+    ``num_scalars``.  Returns (N, Z, C).
+    """
+    del y_parity  # only read under SENDER ordering
+    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic)
+    return _ConvFn.apply(x, y, s, plan, graph)
+
+
+def convolution_bwd(coef, x, y, s, sender, receiver, dm, params, graph_ordering="RECEIVER", y_parity=None,
+                    *, force_generic: bool = False):  # fmt: skip
+    """Cotangents ``(dx, dy, ds)`` for the output cotangent ``dm``; ``coef`` is the
+    *forward* table, as in src/e3j/ops/convolution.py:334-365."""
+    del y_parity
+    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic)
+    return _ConvBwdFn.apply(x, y, s, dm.contiguous(), plan, graph)
+
+
+convolution.Params = CUDAConvolutionParams
+
+
+def get_device_properties() -> dict:
+    """Same keys as ``e3j_ops.get_device_properties()`` (lib/e3j_ops/ffi/e3j_ops.cpp:30-52)."""
+    out = (ctypes.c_int32 * 7)()
+    _lib.check(_lib.lib().e3j_b200_get_device_properties(out))
+    keys = ("device", "smem_max", "smem_opt_in", "smem_per_sm", "max_threads_per_sm", "max_blocks_per_sm", "regs_per_sm")
+    return dict(zip(keys, (int(v) for v in out)))
+
+
+def coef4d_from_table(values: np.ndarray, indices: np.ndarray, mix_idx: np.ndarray) -> Coef4D:
+    idx = np.asarray(indices)
+    l_col = np.asarray(mix_idx).astype(idx.dtype)[idx[:, 0].astype(np.int64)]
+    return Coef4D(values, np.concatenate([idx, l_col[:, None]], axis=-1), val_dtype=np.float32, idx_dtype=idx.dtype)

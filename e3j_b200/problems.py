@@ -1,0 +1,177 @@
+"""Seeded synthetic workloads: point clouds, radius graphs and operator inputs.
+
+Stand-ins for molecular / materials graphs with the shapes, sizes and value
+distributions of the five benchmark configurations:
+
+  0  512 nodes, open cube of side (N / 0.1)^(1/3) A, cutoff 4.5 A, x = 0e+1o
+  1  4096 nodes, same density and cutoff, x = 0e+1o
+  2  25 000 nodes, periodic cube at 0.1 A^-3, cutoff 5 A, x = 0e+1o+2e+3o
+  3  1024 molecules of 10..40 atoms, min distance 0.9 A, cutoff 5 A, concatenated and
+     padded to multiples of 128 nodes / edges with DUMMY_INDEX edges
+  4  1 048 576 nodes, periodic cube at 0.1 A^-3, cutoff 5 A (slab-partitioned)
+
+Edges are directed (every ordered pair within the cutoff, no self loops) and
+sorted by receiver (stable).  The edge vector is ``pos[receiver] - pos[sender]``
+(minimum image under periodic boundaries).  Random draws come from
+``numpy.random.default_rng(seed)``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .graph import DUMMY_INDEX
+from .harmonics import Harmonics
+from .radial import RadialMLP, bessel_envelope_np
+
+DENSITY = 0.1  # atoms per cubic Angstrom
+
+X_IRREPS = {0: "0e+1o", 1: "0e+1o", 2: "0e+1o+2e+3o", 3: "0e+1o+2e+3o", 4: "0e+1o+2e+3o"}
+Y_IRREPS = "0e+1o+2e+3o"
+OUT_FILTER = "0e+1o+2e+3o"
+CUTOFF = {0: 4.5, 1: 4.5, 2: 5.0, 3: 5.0, 4: 5.0}
+NUM_NODES = {0: 512, 1: 4096, 2: 25_000, 4: 1_048_576}
+PERIODIC = {0: False, 1: False, 2: True, 3: False, 4: True}
+
+
+@dataclass
+class Graph:
+    num_nodes: int
+    positions: np.ndarray  # (N, 3) float64
+    sender: np.ndarray  # (E,) int32, DUMMY_INDEX for padding
+    receiver: np.ndarray  # (E,) int32 sorted, DUMMY_INDEX for padding
+    vectors: np.ndarray  # (E, 3) float64, pos[receiver] - pos[sender]; unit x for padding
+    box: float | None = None
+    num_real_nodes: int = 0
+    num_real_edges: int = 0
+    meta: dict = field(default_factory=dict)
+
+
+def radius_graph(pos: np.ndarray, cutoff: float, box: float | None = None):
+    """Directed radius graph sorted by receiver; returns (sender, receiver, vectors)."""
+    from scipy.spatial import cKDTree
+
+    n = pos.shape[0]
+    if box is not None:
+        pos_w = np.mod(pos, box)
+        pos_w[pos_w >= box] -= box  # guard against round-up to the box edge
+        tree = cKDTree(pos_w, boxsize=box)
+    else:
+        pos_w = pos
+        tree = cKDTree(pos)
+    pairs = tree.query_pairs(cutoff, output_type="ndarray")
+    snd = np.concatenate([pairs[:, 0], pairs[:, 1]])
+    rcv = np.concatenate([pairs[:, 1], pairs[:, 0]])
+    order = np.lexsort((snd, rcv))  # receiver major, sender minor: deterministic
+    snd, rcv = snd[order], rcv[order]
+    vec = pos_w[rcv] - pos_w[snd]
+    if box is not None:
+        vec -= box * np.round(vec / box)
+    assert n < DUMMY_INDEX
+    return snd.astype(np.int32), rcv.astype(np.int32), vec
+
+
+def cube_graph(num_nodes: int, cutoff: float, periodic: bool, seed: int = 0) -> Graph:
+    rng = np.random.default_rng(seed)
+    side = (num_nodes / DENSITY) ** (1.0 / 3.0)
+    pos = rng.uniform(0.0, side, size=(num_nodes, 3))
+    snd, rcv, vec = radius_graph(pos, cutoff, side if periodic else None)
+    return Graph(num_nodes, pos, snd, rcv, vec, side if periodic else None, num_nodes, snd.shape[0],
+                 {"side": side, "cutoff": cutoff, "periodic": periodic, "seed": seed})  # fmt: skip
+
+
+def _molecule(rng, n: int, min_dist: float = 0.9) -> np.ndarray:
+    """Rejection sampling in a sphere of radius 0.6 n^(1/3) 1.5 A with a minimum distance."""
+    radius = 0.6 * n ** (1.0 / 3.0) * 1.5
+    pts = np.zeros((0, 3))
+    while pts.shape[0] < n:
+        cand = rng.uniform(-radius, radius, size=3)
+        if np.dot(cand, cand) > radius * radius:
+            continue
+        if pts.shape[0] and np.min(np.sum((pts - cand) ** 2, axis=1)) < min_dist * min_dist:
+            continue
+        pts = np.vstack([pts, cand])
+    return pts
+
+
+def molecules_graph(num_molecules: int = 1024, seed: int = 0, cutoff: float = 5.0, pad_to: int = 128) -> Graph:
+    rng = np.random.default_rng(seed)
+    sizes = rng.integers(10, 41, size=num_molecules)
+    pos, snd, rcv, vec = [], [], [], []
+    offset = 0
+    for n in sizes:
+        p = _molecule(rng, int(n))
+        a, b, v = radius_graph(p, cutoff)
+        pos.append(p + 100.0 * len(pos))  # spread molecules apart; only vectors matter
+        snd.append(a + offset)
+        rcv.append(b + offset)
+        vec.append(v)
+        offset += int(n)
+    pos, snd, rcv, vec = np.concatenate(pos), np.concatenate(snd), np.concatenate(rcv), np.concatenate(vec)
+    n_real, e_real = pos.shape[0], snd.shape[0]
+    n_pad = -(-n_real // pad_to) * pad_to
+    e_pad = -(-e_real // pad_to) * pad_to
+    pos = np.concatenate([pos, np.zeros((n_pad - n_real, 3))])
+    fill = np.full(e_pad - e_real, DUMMY_INDEX, np.int32)
+    unit = np.tile(np.array([[1.0, 0.0, 0.0]]), (e_pad - e_real, 1))
+    return Graph(n_pad, pos, np.concatenate([snd.astype(np.int32), fill]), np.concatenate([rcv.astype(np.int32), fill]),
+                 np.concatenate([vec, unit]), None, n_real, e_real,
+                 {"cutoff": cutoff, "molecules": num_molecules, "seed": seed})  # fmt: skip
+
+
+def make_graph(config: int, seed: int = 0, num_nodes: int | None = None) -> Graph:
+    if config == 3:
+        return molecules_graph(seed=seed)
+    n = num_nodes or NUM_NODES[config]
+    return cube_graph(n, CUTOFF[config], PERIODIC[config], seed)
+
+
+@dataclass
+class Inputs:
+    x: np.ndarray  # (N, X, C) float32
+    y: np.ndarray  # (E, Y) float32
+    s: np.ndarray  # (E, S, C) float32
+    rbf: np.ndarray  # (E, B) float32
+    mlp: RadialMLP
+
+
+def make_inputs(graph: Graph, config: int, num_scalars: int, num_x: int, channels: int = 128, seed: int = 0,
+                hidden: int = 64, num_basis: int = 8) -> Inputs:  # fmt: skip
+    """x ~ N(0, 1); y = component-normalised harmonics of the unit edge vectors up to
+    l = 3; s = radial MLP of the enveloped Bessel basis of the edge length."""
+    rng = np.random.default_rng(seed + 1)
+    x = rng.standard_normal((graph.num_nodes, num_x, channels), dtype=np.float32)
+    y = Harmonics(3, normalize=True, normalization="component")(graph.vectors).astype(np.float32)
+    r = np.linalg.norm(graph.vectors, axis=1)
+    rbf = bessel_envelope_np(r, CUTOFF[config], num_basis).astype(np.float32)
+    mlp = RadialMLP.init(num_basis, hidden, num_scalars * channels, seed)
+    s = np.empty((graph.vectors.shape[0], num_scalars * channels), np.float32)
+    for b in range(0, s.shape[0], 65536):
+        s[b : b + 65536] = mlp.forward_np(rbf[b : b + 65536], np.float32)
+    return Inputs(x, y, s.reshape(-1, num_scalars, channels), rbf, mlp)
+
+
+def make_inputs_device(graph: Graph, config: int, num_scalars: int, num_x: int, device, channels: int = 128,
+                       seed: int = 0, hidden: int = 64, num_basis: int = 8):  # fmt: skip
+    """Same recipe as :func:`make_inputs` with ``x`` drawn and ``s`` evaluated on
+    ``device`` (the [E, S, C] tensor is tens of GB at the larger configurations).
+    Returns torch tensors ``(x, y, s, rbf)`` plus the MLP weights."""
+    import torch
+
+    from .radial import SILU_2MOM
+
+    gen = torch.Generator(device=device).manual_seed(seed + 1)
+    x = torch.randn((graph.num_nodes, num_x, channels), generator=gen, device=device, dtype=torch.float32)
+    y = torch.as_tensor(Harmonics(3, normalize=True, normalization="component")(graph.vectors).astype(np.float32)).to(device)
+    r = np.linalg.norm(graph.vectors, axis=1)
+    rbf = torch.as_tensor(bessel_envelope_np(r, CUTOFF[config], num_basis).astype(np.float32)).to(device)
+    mlp = RadialMLP.init(num_basis, hidden, num_scalars * channels, seed)
+    w1, w2 = torch.as_tensor(mlp.w1).to(device), torch.as_tensor(mlp.w2).to(device)
+    s = torch.empty((rbf.shape[0], num_scalars * channels), device=device, dtype=torch.float32)
+    step = 1 << 18
+    for b in range(0, rbf.shape[0], step):
+        h = SILU_2MOM * torch.nn.functional.silu(rbf[b : b + step] @ w1 / np.sqrt(num_basis))
+        torch.matmul(h, w2 / np.sqrt(hidden), out=s[b : b + step])
+    return x, y, s.view(-1, num_scalars, channels), rbf, mlp

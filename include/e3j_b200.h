@@ -1,0 +1,146 @@
+/*
+ * e3j_b200 — C ABI of the B200 fused message-passing convolution.
+ *
+ * Drop-in boundary for the two XLA-FFI custom-call targets of the reference,
+ * "convolution" and "convolution_bwd" (lib/e3j_ops/ffi/e3j_ops.h:379-472 and
+ * :478-594, registered at src/e3j/ops/__init__.py:15-24).  Every entry point
+ * takes plain device pointers, sizes and a CUDA stream; nothing here depends
+ * on torch, JAX or XLA types.  All work is enqueued on `stream`; no entry
+ * point synchronises unless `debug > 0` (lib/e3j_ops/cuda/convolution/
+ * launch_fwd.cuh:259-263).  Result buffers may arrive uninitialised: every
+ * element of every result is written.
+ *
+ * Layouts (row-major, channel axis last and contiguous):
+ *   x   float[N, X, C]   node features        y   float[E, Y]     edge harmonics
+ *   s   float[E, S, C]   per-edge scalars     out float[N, Z, C]  receiver messages
+ *   sender        int32[E]      sender of each edge, edges sorted by receiver
+ *   receiver_ptr  int32[N + 1]  CSR offsets of the receiver segments
+ * An edge whose sender is outside [0, N) is padding and contributes nothing;
+ * edges at or beyond receiver_ptr[N] belong to no receiver.
+ *
+ * Errors: functions return 0 on success or one of the E3J_B200_* codes below,
+ * which mirror e3j::Error (lib/e3j_ops/ffi/error.h:25-104); the message of the
+ * last failure on the calling thread is available from e3j_b200_last_error()
+ * and carries the same "E3J_ERROR[...]" prefix.  Nothing throws.
+ *
+ * Threading: entry points are re-entrant; a plan may be used concurrently
+ * from several host threads on the device it was created on.
+ */
+#ifndef E3J_B200_H_
+#define E3J_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *e3j_b200_stream; /* == cudaStream_t */
+
+enum {
+    E3J_B200_OK = 0,
+    E3J_B200_INTERNAL = 1,
+    E3J_B200_INVALID_ARGUMENT = 2,
+    E3J_B200_CUDA_LAUNCH = 3,
+    E3J_B200_CUDA_RUNTIME = 4,
+    E3J_B200_UNIMPLEMENTED = 5
+};
+
+/* Kernel variants a plan can resolve to. */
+enum {
+    E3J_B200_VARIANT_GENERIC = 0, /* table-driven, any irreps, any C */
+    E3J_B200_VARIANT_L1_L3 = 1,   /* unrolled: x = 0e+1o, y = 0e..3o, out l<=3, C = 128 */
+    E3J_B200_VARIANT_L3_L3 = 2    /* unrolled: x = 0e..3o, y = 0e..3o, out l<=3, C = 128 */
+};
+
+const char *e3j_b200_last_error(void);
+
+/* Library build information: "e3j_b200 <version> sm_100a". */
+const char *e3j_b200_version(void);
+
+/*
+ * Device limits the reference's host-side launch heuristics read through
+ * e3j_ops.get_device_properties() (lib/e3j_ops/ffi/e3j_ops.cpp:30-52):
+ * fills out[0..6] = {device, smem_max, smem_opt_in, smem_per_sm,
+ * max_threads_per_sm, max_blocks_per_sm, regs_per_sm} for the current device.
+ */
+int e3j_b200_get_device_properties(int32_t out[7]);
+
+/* ------------------------------------------------------------------------ *
+ * Plans.  A plan is the host-side analysis of one packed Coef4D table
+ * (src/e3j/ops/coef.py:228-235; rows {float val; Idx i, j, k, l} with
+ * i = output row, j = x row, k = y component, l = scalar index), made once
+ * where the reference packs and balances its table at trace time
+ * (src/e3j/ops/convolution.py:166-208).  `coef_host` is HOST memory with
+ * `nnz` rows of Idx = uint8 (idx_bytes = 1, 8-byte rows) or int32
+ * (idx_bytes = 4, 32-byte rows).  Creation uploads the derived tables to
+ * the current device (it allocates and synchronises; call it at set-up, not
+ * inside a stream capture).  A table whose sparsity pattern matches one of
+ * the unrolled variants and C == 128 resolves to that variant unless
+ * `force_generic` is non-zero; values always come from the table.
+ * ------------------------------------------------------------------------ */
+typedef struct e3j_b200_plan e3j_b200_plan;
+
+int e3j_b200_plan_create(const void *coef_host, int32_t nnz, int32_t idx_bytes, int32_t X,
+                         int32_t Y, int32_t Z, int32_t S, int32_t C, int32_t force_generic,
+                         e3j_b200_plan **plan);
+void e3j_b200_plan_destroy(e3j_b200_plan *plan);
+int e3j_b200_plan_variant(const e3j_b200_plan *plan);
+
+/*
+ * Forward: out[r, i, c] = sum_{e in segment r} sum_n val_n x[sender[e], j_n, c] y[e, k_n] s[e, l_n, c].
+ * Replaces the "convolution" target (lib/e3j_ops/ffi/e3j_ops.h:379-472) and
+ * e3j::convolution::launch (lib/e3j_ops/cuda/convolution/launch_fwd.cuh:204-266).
+ * Deterministic: no atomics, fixed summation order.
+ */
+int e3j_b200_conv_fwd(const e3j_b200_plan *plan, const float *x, const float *y, const float *s,
+                      const int32_t *sender, const int32_t *receiver_ptr, float *out, int32_t N,
+                      int64_t E, int32_t debug, e3j_b200_stream stream);
+
+/*
+ * Backward: cotangents dx[N, X, C], dy[E, Y], ds[E, S, C] of the forward for
+ * the output cotangent dm[N, Z, C].  Replaces the "convolution_bwd" target
+ * (lib/e3j_ops/ffi/e3j_ops.h:478-594) and e3j::convolution::launch_bwd
+ * (lib/e3j_ops/cuda/convolution/launch_bwd.cuh:202-265).
+ *
+ * Graph operands: `sender` / `receiver_ptr` as in the forward, plus the
+ * sender-sorted view the reference derives with GraphCSR.transpose()
+ * (src/e3j/data/graph.py:59-72): `sender_ptr_t` int32[N + 1] and
+ * `perm_t` int32[E] with perm_t[p] = original index of the p-th edge in
+ * sender order (positions at or beyond sender_ptr_t[N] are ignored).
+ *
+ * `workspace` is caller-owned device scratch of at least
+ * e3j_b200_conv_bwd_workspace_bytes() bytes, 256-byte aligned; it holds the
+ * per-edge dx messages between the two passes.  dy and ds of padding edges and
+ * dx rows of nodes that send nothing are exact zeros.  Deterministic.
+ */
+size_t e3j_b200_conv_bwd_workspace_bytes(const e3j_b200_plan *plan, int32_t N, int64_t E);
+
+int e3j_b200_conv_bwd(const e3j_b200_plan *plan, const float *x, const float *y, const float *s,
+                      const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                      const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                      float *ds, void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
+                      int32_t debug, e3j_b200_stream stream);
+
+/*
+ * Same as e3j_b200_conv_bwd, restricted to the passes selected by `phases`
+ * (bit 0: per-edge pass writing ds, dy and the dx messages; bit 1: zero fill of
+ * the edges beyond receiver_ptr[N]; bit 2: per-sender sum of the dx messages).
+ * Lets a profiler or benchmark bracket each pass with its own events; the
+ * passes must run in bit order on one stream.  No counterpart in the
+ * reference, whose backward is a single kernel.
+ */
+enum { E3J_B200_BWD_EDGES = 1, E3J_B200_BWD_TAIL = 2, E3J_B200_BWD_DX = 4, E3J_B200_BWD_ALL = 7 };
+
+int e3j_b200_conv_bwd_phases(const e3j_b200_plan *plan, const float *x, const float *y,
+                             const float *s, const float *dm, const int32_t *sender,
+                             const int32_t *receiver_ptr, const int32_t *sender_ptr_t,
+                             const int32_t *perm_t, float *dx, float *dy, float *ds,
+                             void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
+                             int32_t debug, e3j_b200_stream stream, int32_t phases);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* E3J_B200_H_ */

@@ -1,0 +1,79 @@
+"""TEST INFRASTRUCTURE: numpy restatement of the unfused convolution and its VJP.
+
+Follows the reference's plain-JAX path step by step:
+  gather ``x[senders]``                       src/e3j/core/convolution.py:181
+  sparse CG product (gather columns, multiply,
+  scatter-add on the output coordinate)       src/e3j/core/tensor_product.py:300-319,
+                                              src/e3j/utils/sparse.py:259-268
+  scalar mixing ``s[:, mix_idx] * features``  src/e3j/core/scalar_mixing.py:88-91
+  scatter-add on receivers                    src/e3j/core/convolution.py:184-191
+and the compact form used by the reference's op tests
+(tests/test_ops/test_convolution_op.py:56-70).  The VJP is the exact
+derivative of that expression (formulas as in
+src/e3j/pallas_ops/convolution/mosaic_gpu/bwd.py:596-608).
+
+Edges are processed in chunks so the [E, Z, C] message tensor is never
+materialised.  Edges with an endpoint outside [0, N) contribute nothing and
+receive zero dy / ds.  Computation dtype is that of ``dtype`` (float64 gives
+the truth used for tolerance checks).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def _onehot(idx: np.ndarray, n: int, dtype) -> np.ndarray:
+    m = np.zeros((n, idx.shape[0]), dtype=dtype)
+    m[idx, np.arange(idx.shape[0])] = 1
+    return m
+
+
+def conv_fwd(val, idx4, x, y, s, sender, receiver, num_out, *, dtype=np.float64, chunk=4096):
+    """out[N, Z, C]; ``idx4`` is (nnz, 4) = (i, j, k, l)."""
+    val = np.asarray(val, dtype)
+    idx4 = np.asarray(idx4, np.int64)
+    x, y, s = (np.asarray(a, dtype) for a in (x, y, s))
+    n_nodes, _, ch = x.shape
+    sender = np.asarray(sender, np.int64)
+    receiver = np.asarray(receiver, np.int64)
+    ok = (sender >= 0) & (sender < n_nodes) & (receiver >= 0) & (receiver < n_nodes)
+    out = np.zeros((n_nodes, num_out, ch), dtype)
+    scat = _onehot(idx4[:, 0], num_out, dtype)  # [Z, nnz]
+    edges = np.nonzero(ok)[0]
+    for b in range(0, edges.size, chunk):
+        e = edges[b : b + chunk]
+        xe = x[sender[e]]
+        terms = val[None, :, None] * xe[:, idx4[:, 1], :] * y[e][:, idx4[:, 2], None]
+        terms = terms * s[e][:, idx4[:, 3], :]
+        msg = np.einsum("zn,enc->ezc", scat, terms)
+        np.add.at(out, receiver[e], msg)
+    return out
+
+
+def conv_bwd(val, idx4, x, y, s, dm, sender, receiver, *, dtype=np.float64, chunk=4096):
+    """(dx[N, X, C], dy[E, Y], ds[E, S, C])."""
+    val = np.asarray(val, dtype)
+    idx4 = np.asarray(idx4, np.int64)
+    x, y, s, dm = (np.asarray(a, dtype) for a in (x, y, s, dm))
+    n_nodes, nx, ch = x.shape
+    sender = np.asarray(sender, np.int64)
+    receiver = np.asarray(receiver, np.int64)
+    ok = (sender >= 0) & (sender < n_nodes) & (receiver >= 0) & (receiver < n_nodes)
+    dx = np.zeros_like(x)
+    dy = np.zeros_like(y)
+    ds = np.zeros_like(s)
+    sj = _onehot(idx4[:, 1], nx, dtype)
+    sk = _onehot(idx4[:, 2], y.shape[1], dtype)
+    sl = _onehot(idx4[:, 3], s.shape[1], dtype)
+    edges = np.nonzero(ok)[0]
+    for b in range(0, edges.size, chunk):
+        e = edges[b : b + chunk]
+        xj = x[sender[e]][:, idx4[:, 1], :]
+        yk = y[e][:, idx4[:, 2], None]
+        slv = s[e][:, idx4[:, 3], :]
+        g = val[None, :, None] * dm[receiver[e]][:, idx4[:, 0], :]
+        np.add.at(dx, sender[e], np.einsum("jn,enc->ejc", sj, g * yk * slv))
+        dy[e] = np.einsum("kn,en->ek", sk, np.sum(g * xj * slv, axis=-1))
+        ds[e] = np.einsum("ln,enc->elc", sl, g * xj * yk)
+    return dx, dy, ds

@@ -1,0 +1,66 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# fp32 tolerance of the convolution path: |got - want| <= ATOL + RTOL * scale, where
+# `want` is the float64 oracle and `scale` is the magnitude of the compared tensor
+# (max |want|): sums of ~nnz * degree fp32 products are compared, so the bound is
+# relative to the size of the terms, as the reference does when it widens its
+# own tolerance with the degree (tests/test_ops/test_convolution_op.py:314-320).
+RTOL = 1e-5
+ATOL = 1e-6
+
+
+def assert_close(got, want, rtol=RTOL, atol=ATOL, what=""):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
+    assert np.isfinite(got).all(), f"{what}: non-finite values"
+    scale = float(np.abs(want).max()) if want.size else 0.0
+    err = float(np.abs(got - want).max()) if want.size else 0.0
+    assert err <= atol + rtol * max(scale, 1.0), f"{what}: max abs err {err:.3e} (scale {scale:.3e})"
+
+
+def random_table(rng, nnz, nx, ny, nz, ns):
+    """Random coefficient table sorted by (i, j, k) with l = mix(i), like the
+    reference's op tests (tests/test_ops/test_convolution_op.py:110-150)."""
+    flat = rng.choice(nz * nx * ny, size=min(nnz, nz * nx * ny), replace=False)
+    flat.sort()
+    i, j, k = np.unravel_index(flat, (nz, nx, ny))
+    mix = np.sort(rng.integers(0, ns, size=nz))
+    val = rng.standard_normal(len(flat)).astype(np.float32)
+    return val, np.stack([i, j, k, mix[i]], axis=-1).astype(np.int32)
+
+
+def random_graph(rng, num_nodes, num_edges):
+    snd = rng.integers(0, num_nodes, size=num_edges)
+    rcv = np.sort(rng.integers(0, num_nodes, size=num_edges))
+    return snd.astype(np.int32), rcv.astype(np.int32)
+
+
+def csr_ptr(receiver, num_nodes):
+    r = np.asarray(receiver, np.int64)
+    r = r[(r >= 0) & (r < num_nodes)]
+    return np.concatenate([[0], np.cumsum(np.bincount(r, minlength=num_nodes))]).astype(np.int32)

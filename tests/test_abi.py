@@ -1,0 +1,54 @@
+"""The C-ABI library builds, loads and exports every declared symbol."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from e3j_b200 import _lib
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(__file__)), "include", "e3j_b200.h")
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    return sorted(set(re.findall(r"\b(e3j_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    _lib.build()
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    names = declared_functions()
+    assert names, "no declarations found"
+    for name in names:
+        assert hasattr(handle, name), f"{name} is declared in include/e3j_b200.h but not exported"
+    assert sorted(_lib.EXPORTED_SYMBOLS) == names
+
+
+def test_version_and_error_string():
+    lib = _lib.lib()
+    assert lib.e3j_b200_version().decode().startswith("e3j_b200 ")
+    assert isinstance(lib.e3j_b200_last_error(), bytes)
+
+
+def test_cpu_tensors_are_rejected():
+    import numpy as np
+    import torch
+
+    from e3j_b200.convolution import Convolution
+
+    conv = Convolution(("0e", "0e"), None, graph_ordering="RECEIVER")
+    x = torch.zeros(2, 1, 4)
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        conv(x, torch.zeros(1, 1), torch.zeros(1, 1, 4), torch.tensor([0]), torch.tensor([1]))
+    with pytest.raises(NotImplementedError):
+        conv(torch.zeros(2, 1, 3), torch.zeros(1, 1), torch.zeros(1, 1, 3), torch.tensor([0]), torch.tensor([1]))
+    assert np.dtype(conv.coef.idx.dtype) == np.uint8
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.LibraryMissing):
+        _lib.lib()

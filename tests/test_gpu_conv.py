@@ -1,0 +1,298 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from e3j_b200 import ops, problems
+from e3j_b200.coef import Coef4D
+from e3j_b200.convolution import Convolution
+from oracle import c_oracle, numpy_oracle
+from tests.conftest import assert_close, csr_ptr, random_graph, random_table
+from tests.golden import strip_fixture
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "conv_small.npz")
+
+
+def dev(a, dtype=None):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype).to(DEV)
+
+
+def run_raw(val, idx4, x, y, s, snd, rcv, nz, dm=None, *, idx_dtype="int32", force_generic=False, poison=False):
+    """Forward (and backward when dm is given) through e3j_b200_conv_fwd / _bwd."""
+    coef = Coef4D(val, idx4, idx_dtype=idx_dtype).pack()
+    dims = (x.shape[1], y.shape[1], nz, s.shape[1], x.shape[2])
+    plan = ops.get_plan(coef, dims, torch.device(DEV), force_generic)
+    n = x.shape[0]
+    graph = ops.ConvGraph.build(n, dev(snd), dev(rcv))
+    tx, ty, ts = dev(x), dev(y), dev(s)
+    out = ops.conv_fwd_raw(plan, tx, ty, ts, graph)
+    if dm is None:
+        return out.cpu().numpy(), plan
+    ws = None
+    if poison:
+        need = ops._lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, y.shape[0])
+        ws = torch.full((need // 4 + 64,), float("nan"), device=DEV).view(torch.uint8)
+    dx, dy, ds = ops.conv_bwd_raw(plan, tx, ty, ts, dev(dm), graph, ws)
+    torch.cuda.synchronize()
+    return (out.cpu().numpy(), dx.cpu().numpy(), dy.cpu().numpy(), ds.cpu().numpy()), plan
+
+
+@pytest.mark.parametrize("strips,channels,scale", strip_fixture.CASES)
+@pytest.mark.parametrize("idx_dtype", ["uint8", "int32"])
+def test_reference_fixture_exact(strips, channels, scale, idx_dtype):
+    f = strip_fixture.make(strips, channels, scale)
+    (out, dx, dy, ds), _ = run_raw(f["val"], f["idx4"], f["x"], f["y"], f["s"], f["sender"], f["receiver"],
+                                   f["num_out"], f["dz"], idx_dtype=idx_dtype)  # fmt: skip
+    assert (out == f["out"]).all()
+    assert (dx == f["dx"]).all() and (dy == f["dy"]).all() and (ds == f["ds"]).all()
+
+
+def test_committed_vectors():
+    g = np.load(GOLDEN)
+    (out, dx, dy, ds), _ = run_raw(g["val"], g["idx4"], g["x"], g["y"], g["s"], g["sender"], g["receiver"],
+                                   g["out"].shape[1], g["dm"])  # fmt: skip
+    for got, name in ((out, "out"), (dx, "dx"), (dy, "dy"), (ds, "ds")):
+        assert_close(got, g[name], what=name)
+
+
+# channel sweep of the reference's op tests (tests/test_ops/test_convolution_op.py:215-301)
+@pytest.mark.parametrize("channels", [1, 2, 4, 8, 16, 32, 64, 128, 256, 512])
+def test_random_tables(channels):
+    rng = np.random.default_rng(channels)
+    n, e, nx, ny, nz, ns = 8, 24, 6, 5, 11, 4
+    val, idx4 = random_table(rng, 60, nx, ny, nz, ns)
+    snd, rcv = random_graph(rng, n, e)
+    x, y, s, dm = (rng.standard_normal(sh).astype(np.float32) for sh in [(n, nx, channels), (e, ny), (e, ns, channels), (n, nz, channels)])
+    (out, dx, dy, ds), _ = run_raw(val, idx4, x, y, s, snd, rcv, nz, dm)
+    ptr = csr_ptr(rcv, n)
+    ptr_t, perm_t = c_oracle.transpose_csr(snd, n)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, x, y, s, snd, ptr, nz), what="out")
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, x, y, s, dm, snd, ptr, ptr_t, perm_t)
+    assert_close(dx, wdx, what="dx")
+    assert_close(dy, wdy, what="dy")
+    assert_close(ds, wds, what="ds")
+
+
+def test_large_irreps_accumulate_in_the_result_row():
+    """More output rows than shared memory holds."""
+    rng = np.random.default_rng(7)
+    n, e, nx, ny, nz, ns, c = 5, 12, 3, 4, 600, 7, 128
+    val, idx4 = random_table(rng, 900, nx, ny, nz, ns)
+    snd, rcv = random_graph(rng, n, e)
+    x, y, s = (rng.standard_normal(sh).astype(np.float32) for sh in [(n, nx, c), (e, ny), (e, ns, c)])
+    out, _ = run_raw(val, idx4, x, y, s, snd, rcv, nz)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, x, y, s, snd, csr_ptr(rcv, n), nz))
+
+
+def _module_case(config, n_nodes, channels=128, seed=0):
+    x_irreps = problems.X_IRREPS[config]
+    conv = Convolution((x_irreps, problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER", avg_num_neighbors=30.0)
+    g = problems.make_graph(config, seed, num_nodes=n_nodes)
+    inp = problems.make_inputs(g, config, conv.num_scalars, conv.source[0].dim, channels, seed)
+    return conv, g, inp
+
+
+@pytest.mark.parametrize("config,n_nodes", [(0, 512), (2, 600)])
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_module_forward_backward(config, n_nodes, force_generic):
+    """`Convolution.__call__` + autograd with the real CG table, lmax = 3, 128 channels,
+    loss = sum(out^2) as in the benchmark configurations."""
+    conv, g, inp = _module_case(config, n_nodes)
+    conv.force_generic = force_generic
+    x, y, s = (dev(a).requires_grad_() for a in (inp.x, inp.y, inp.s))
+    out = conv(x, y, s, dev(g.sender), dev(g.receiver))
+    (out * out).sum().backward()
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    want = c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, g.sender, ptr, conv.target.dim)
+    assert_close(out.detach().cpu().numpy(), want, what="out")
+    ptr_t, perm_t = c_oracle.transpose_csr(g.sender, g.num_nodes)
+    dm = 2 * out.detach().cpu().numpy()
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, inp.x, inp.y, inp.s, dm, g.sender, ptr, ptr_t, perm_t)
+    assert_close(x.grad.cpu().numpy(), wdx, what="dx")
+    assert_close(y.grad.cpu().numpy(), wdy, what="dy")
+    assert_close(s.grad.cpu().numpy(), wds, what="ds")
+    plan = ops.get_plan(conv._coef_packed, (conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128),
+                        torch.device(DEV), force_generic)  # fmt: skip
+    assert (plan.variant == 0) == force_generic
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_padding_empty_rows_and_poisoned_memory(force_generic):
+    """Padding edges are skipped, rows without edges are exact zeros, cotangents of
+    padding edges are exact zeros even when result and scratch memory hold NaN
+    (tests/test_ops/test_convolution_jax_transforms.py:230-306 of the reference)."""
+    conv, g, inp = _module_case(0, 200)
+    big = problems.DUMMY_INDEX
+    n, e = g.num_nodes, g.sender.shape[0]
+    snd, rcv = g.sender.copy(), g.receiver.copy()
+    # drop every edge into node 3 / out of node 5, make edge 10 an in-segment padding edge
+    snd[10] = big
+    pad = 7
+    snd = np.concatenate([snd, [big] * pad]).astype(np.int32)
+    rcv = np.concatenate([rcv, [big] * pad]).astype(np.int32)
+    y = np.concatenate([inp.y, np.full((pad, 16), np.nan, np.float32)])
+    s = np.concatenate([inp.s, np.full((pad,) + inp.s.shape[1:], np.nan, np.float32)])
+    x = np.concatenate([inp.x, np.zeros((2,) + inp.x.shape[1:], np.float32)])  # two isolated trailing nodes
+    n2 = n + 2
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    dm = np.random.default_rng(0).standard_normal((n2, conv.target.dim, 128)).astype(np.float32)
+    (out, dx, dy, ds), _ = run_raw(val, idx4, x, y, s, snd, rcv, conv.target.dim, dm, idx_dtype="uint8",
+                                   force_generic=force_generic, poison=True)  # fmt: skip
+    ptr = csr_ptr(rcv, n2)
+    ptr_t, perm_t = c_oracle.transpose_csr(snd, n2)
+    y0, s0 = np.nan_to_num(y), np.nan_to_num(s)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, x, y0, s0, snd, ptr, conv.target.dim), what="out")
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, x, y0, s0, dm, snd, ptr, ptr_t, perm_t)
+    assert_close(dx, wdx, what="dx")
+    assert_close(dy, wdy, what="dy")
+    assert_close(ds, wds, what="ds")
+    assert (out[n:] == 0).all() and (dx[n:] == 0).all()
+    assert (dy[e:] == 0).all() and (ds[e:] == 0).all() and (dy[10] == 0).all() and (ds[10] == 0).all()
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_bitwise_determinism(force_generic):
+    """Repeated runs agree bit for bit, forward and backward
+    (tests/test_ops/test_convolution_op.py:322-342 of the reference)."""
+    conv, g, inp = _module_case(2, 400)
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    dm = np.random.default_rng(1).standard_normal((g.num_nodes, conv.target.dim, 128)).astype(np.float32)
+    first = None
+    for _ in range(10):
+        res, _ = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, conv.target.dim, dm,
+                         idx_dtype="uint8", force_generic=force_generic)  # fmt: skip
+        if first is None:
+            first = res
+        else:
+            for a, b in zip(first, res):
+                assert np.array_equal(a, b)
+
+
+def test_molecule_batch_with_padding():
+    """Short segments, padded node and edge counts (benchmark configuration 3, reduced)."""
+    conv = Convolution((problems.X_IRREPS[3], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER")
+    g = problems.molecules_graph(num_molecules=24, seed=3)
+    inp = problems.make_inputs(g, 3, conv.num_scalars, 16, 128, 3)
+    assert g.num_nodes % 128 == 0 and g.sender.shape[0] % 128 == 0 and g.num_real_edges < g.sender.shape[0]
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    dm = np.random.default_rng(2).standard_normal((g.num_nodes, 99, 128)).astype(np.float32)
+    (out, dx, dy, ds), plan = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, 99, dm, idx_dtype="uint8")
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    ptr_t, perm_t = c_oracle.transpose_csr(g.sender, g.num_nodes)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, g.sender, ptr, 99), what="out")
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, inp.x, inp.y, inp.s, dm, g.sender, ptr, ptr_t, perm_t)
+    assert_close(dx, wdx, what="dx")
+    assert_close(dy, wdy, what="dy")
+    assert_close(ds, wds, what="ds")
+    assert (ds[g.num_real_edges :] == 0).all()
+
+
+def test_node_mask_and_avg_num_neighbors():
+    conv1 = Convolution(("0e+1o", "0e+1o"), None, graph_ordering="RECEIVER")
+    conv4 = Convolution(("0e+1o", "0e+1o"), None, graph_ordering="RECEIVER", avg_num_neighbors=4.0)
+    rng = np.random.default_rng(5)
+    n, e, c = 9, 40, 32
+    snd, rcv = random_graph(rng, n, e)
+    x, y, s = (dev(rng.standard_normal(sh).astype(np.float32)) for sh in [(n, 4, c), (e, 4), (e, conv1.num_scalars, c)])
+    a = conv1(x, y, s, dev(snd), dev(rcv))
+    b = conv4(x, y, s, dev(snd), dev(rcv))
+    assert torch.allclose(a, 4 * b, rtol=1e-6, atol=1e-6)
+    mask = torch.ones(n, dtype=torch.bool, device=DEV)
+    mask[-2:] = False
+    m = conv1(x, y, s, dev(snd), dev(rcv), node_mask=mask)
+    keep = (snd < n - 2) & (rcv < n - 2)
+    want = numpy_oracle.conv_fwd(conv1.coef.val, conv1.coef.idx, x.cpu().numpy(), y.cpu().numpy()[keep],
+                                 s.cpu().numpy()[keep], snd[keep], rcv[keep], conv1.target.dim)  # fmt: skip
+    assert_close(m.cpu().numpy(), want)
+
+
+def test_double_backward_matches_oracle_composition():
+    """Second-order rule (src/e3j/ops/convolution.py:535-562): gradient of <dx, u> + <dy, v> + <ds, w>."""
+    rng = np.random.default_rng(11)
+    conv = Convolution(("0e+1o", "0e+1o+2e"), None, graph_ordering="RECEIVER")
+    n, e, c = 6, 20, 32
+    snd, rcv = random_graph(rng, n, e)
+    nz, ns = conv.target.dim, conv.num_scalars
+    arrs = [rng.standard_normal(sh).astype(np.float32) for sh in [(n, 4, c), (e, 9), (e, ns, c), (n, nz, c)]]
+    x, y, s, dm = (dev(a).requires_grad_() for a in arrs)
+    u, v, w = (dev(rng.standard_normal(t.shape).astype(np.float32)) for t in (x, y, s))
+    out = conv(x, y, s, dev(snd), dev(rcv))
+    dx, dy, ds = torch.autograd.grad(out, (x, y, s), dm, create_graph=True)
+    scalar = (dx * u).sum() + (dy * v).sum() + (ds * w).sum()
+    gx, gy, gs, gdm = torch.autograd.grad(scalar, (x, y, s, dm))
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    f = lambda a, b, c_: numpy_oracle.conv_fwd(val, idx4, a, b, c_, snd, rcv, nz)  # noqa: E731
+    b = lambda a, b_, c_: numpy_oracle.conv_bwd(val, idx4, a, b_, c_, arrs[3], snd, rcv)  # noqa: E731
+    un, vn, wn = (t.cpu().numpy() for t in (u, v, w))
+    want_dm = f(un, arrs[1], arrs[2]) + f(arrs[0], vn, arrs[2]) + f(arrs[0], arrs[1], wn)
+    bx, by, bs = b(un, arrs[1], arrs[2]), b(arrs[0], vn, arrs[2]), b(arrs[0], arrs[1], wn)
+    assert_close(gdm.cpu().numpy(), want_dm, what="Ddm", rtol=2e-5)
+    assert_close(gx.cpu().numpy(), by[0] + bs[0], what="Dx", rtol=2e-5)
+    assert_close(gy.cpu().numpy(), bx[1] + bs[1], what="Dy", rtol=2e-5)
+    assert_close(gs.cpu().numpy(), bx[2] + by[2], what="Ds", rtol=2e-5)
+
+
+@pytest.mark.parametrize("config", [1, 2])
+def test_full_size_adjoint_identities(config):
+    """At the benchmark sizes the oracle is too slow to run in full; the operator is
+    trilinear, so <dm, conv(x, y, s)> = <x, dx> = <y, dy> = <s, ds> must hold, and a
+    sample of receiver rows / edge rows is compared with the oracle directly."""
+    conv = Convolution((problems.X_IRREPS[config], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    g = problems.make_graph(config, 0)
+    x, y, s, _, _ = problems.make_inputs_device(g, config, conv.num_scalars, conv.source[0].dim, torch.device(DEV))
+
+    from types import SimpleNamespace
+
+    inp = SimpleNamespace(x=x.cpu().numpy(), y=y.cpu().numpy())  # host copies of what the oracle samples
+
+    def s_rows(e):
+        return s[torch.as_tensor(e, device=DEV)].cpu().numpy()
+
+    graph = conv.prepare_graph(g.num_nodes, dev(g.sender), dev(g.receiver))
+    plan = ops.get_plan(conv._coef_packed, (conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128), torch.device(DEV))
+    out = ops.conv_fwd_raw(plan, x, y, s, graph)
+    dm = torch.randn_like(out)
+    dx, dy, ds = ops.conv_bwd_raw(plan, x, y, s, dm, graph)
+    ref = (dm.double() * out.double()).sum().item()
+    for a, b in ((x, dx), (y, dy), (s, ds)):
+        got = (a.double() * b.double()).sum().item()
+        assert abs(got - ref) <= 1e-5 * max(abs(ref), (dm.double().abs() * out.double().abs()).sum().item() * 1e-2)
+    # sampled rows against the oracle: a sub-graph made of the edges into 64 receivers
+    rng = np.random.default_rng(0)
+    rows = np.sort(rng.choice(g.num_nodes, 64, replace=False))
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    edges = np.concatenate([np.arange(ptr[r], ptr[r + 1]) for r in rows])
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    sub = numpy_oracle.conv_fwd(val, idx4, inp.x, inp.y[edges], s_rows(edges), g.sender[edges], g.receiver[edges], conv.target.dim)
+    assert_close(out[rows].cpu().numpy(), sub[rows], what="sampled out rows")
+    dmn = dm.cpu().numpy()
+    _, wdy, wds = numpy_oracle.conv_bwd(val, idx4, inp.x, inp.y[edges], s_rows(edges), dmn, g.sender[edges], g.receiver[edges])
+    assert_close(dy[edges].cpu().numpy(), wdy, what="sampled dy rows")
+    assert_close(ds[edges].cpu().numpy(), wds, what="sampled ds rows")
+    # dx rows of 32 senders: all their outgoing edges
+    snd_rows = np.sort(rng.choice(g.num_nodes, 32, replace=False))
+    emask = np.isin(g.sender, snd_rows)
+    wdx, _, _ = numpy_oracle.conv_bwd(val, idx4, inp.x, inp.y[emask], s_rows(np.nonzero(emask)[0]), dmn, g.sender[emask], g.receiver[emask])
+    assert_close(dx[snd_rows].cpu().numpy(), wdx[snd_rows], what="sampled dx rows")
+
+
+def test_errors_are_reported_not_thrown_across_the_abi():
+    import ctypes
+
+    lib = ops._lib.lib()
+    handle = ctypes.c_void_p()
+    bad = np.zeros((1, 8), np.uint8)
+    bad[0, 4] = 200  # output row out of bounds
+    rc = lib.e3j_b200_plan_create(bad.ctypes.data_as(ctypes.c_void_p), 1, 1, 2, 2, 2, 1, 32, 0, ctypes.byref(handle))
+    assert rc == 2 and lib.e3j_b200_last_error().decode().startswith("E3J_ERROR[InvalidArgument]")
+    rc = lib.e3j_b200_plan_create(bad.ctypes.data_as(ctypes.c_void_p), 1, 2, 2, 2, 2, 1, 32, 0, ctypes.byref(handle))
+    assert rc == 2 and "dtype pair" in lib.e3j_b200_last_error().decode()
+    props = ops.get_device_properties()
+    assert props["smem_opt_in"] >= 200 * 1024 and props["regs_per_sm"] == 65536
