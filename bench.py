@@ -277,8 +277,8 @@ def run_ours(args):
         h_loss.copy_(loss.detach(), non_blocking=True)
         h_dx.copy_(gx.grad, non_blocking=True)
 
-    e2e_steps = max(2, min(args.steps, 10))
-    for _ in range(2):
+    e2e_steps = 0 if args.no_e2e else max(2, min(args.steps, 10))
+    for _ in range(0 if args.no_e2e else 2):
         e2e_step()
     barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -287,7 +287,7 @@ def run_ours(args):
         e2e_step()
     b.record()
     barrier()
-    e2e_ms = a.elapsed_time(b) / e2e_steps
+    e2e_ms = a.elapsed_time(b) / max(e2e_steps, 1)
 
     # ---- reduce over ranks: slowest rank, total edges ----
     stats = torch.tensor([ms_total, e2e_ms, float(e_real)], device=device, dtype=torch.float64)
@@ -348,6 +348,7 @@ def main():
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

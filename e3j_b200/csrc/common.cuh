@@ -51,19 +51,88 @@ __device__ __forceinline__ bool in_range(int32_t a, int32_t n) {
     return static_cast<uint32_t>(a) < static_cast<uint32_t>(n);
 }
 
-// Streaming loads/stores: data touched once (s, ds, dy, dx messages) should not
-// displace the node rows (x, dm) that are re-read through L2.
-__device__ __forceinline__ float4 ld_stream4(const float *p) {
-    float4 v;
-    asm volatile("ld.global.L1::no_allocate.L2::evict_first.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p));
-    return v;
+// Streaming store: data written once and not read again by this kernel (ds, dy,
+// dx messages) should not displace the node rows (x, dm) that are re-read through L2.
+__device__ __forceinline__ void st_stream4(float4 *p, float4 v) { __stcs(p, v); }
+
+constexpr unsigned FULL = 0xffffffffu;
+
+// ---- float4 arithmetic -----------------------------------------------------
+__device__ __forceinline__ float4 mul_sv(float s, const float4 &v) {
+    return make_float4(s * v.x, s * v.y, s * v.z, s * v.w);
 }
-__device__ __forceinline__ void st_stream4(float *p, float4 v) {
-    asm volatile("st.global.L1::no_allocate.L2::evict_first.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p),
-                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+__device__ __forceinline__ float4 mul_vv(const float4 &a, const float4 &b) {
+    return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+}
+__device__ __forceinline__ void fma_sv(float4 &d, float s, const float4 &v) {
+    d.x = fmaf(s, v.x, d.x); d.y = fmaf(s, v.y, d.y); d.z = fmaf(s, v.z, d.z); d.w = fmaf(s, v.w, d.w);
+}
+__device__ __forceinline__ void fma_vv(float4 &d, const float4 &a, const float4 &b) {
+    d.x = fmaf(a.x, b.x, d.x); d.y = fmaf(a.y, b.y, d.y); d.z = fmaf(a.z, b.z, d.z); d.w = fmaf(a.w, b.w, d.w);
+}
+__device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
+    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, a.x * b.x)));
+}
+
+// ---- 16-byte asynchronous global -> shared copies (one per lane) ------------
+// `_stream`: the source is read once (s, y): evict-first in L2.
+// `_keep`:   the source is a node row gathered by many edges (x): default L2 policy.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void cp_async16_hint(void *smem_dst, const void *gmem_src, uint64_t policy) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src),
+                 "l"(policy)
                  : "memory");
+}
+__device__ __forceinline__ void cp_async16_stream(void *smem_dst, const void *gmem_src) {
+    cp_async16_hint(smem_dst, gmem_src, l2_policy_evict_first());
+}
+__device__ __forceinline__ void cp_async16_keep(void *smem_dst, const void *gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Sum of 16 per-lane values over the 32 lanes of a warp by a halving butterfly
+// (16 shuffles).  Returns, on every lane, the total of component (lane >> 1) & 15.
+// The tree is fixed, so the result is bitwise reproducible.
+__device__ __forceinline__ float warp_reduce16(const float (&v)[16], int lane) {
+    float a8[8], a4[4], a2[2];
+    bool hi = lane & 16;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float send = hi ? v[i] : v[i + 8], keep = hi ? v[i + 8] : v[i];
+        a8[i] = keep + __shfl_xor_sync(FULL, send, 16);
+    }
+    hi = lane & 8;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float send = hi ? a8[i] : a8[i + 4], keep = hi ? a8[i + 4] : a8[i];
+        a4[i] = keep + __shfl_xor_sync(FULL, send, 8);
+    }
+    hi = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float send = hi ? a4[i] : a4[i + 2], keep = hi ? a4[i + 2] : a4[i];
+        a2[i] = keep + __shfl_xor_sync(FULL, send, 4);
+    }
+    hi = lane & 2;
+    const float send = hi ? a2[0] : a2[1], keep = hi ? a2[1] : a2[0];
+    const float a1 = keep + __shfl_xor_sync(FULL, send, 2);
+    return a1 + __shfl_xor_sync(FULL, a1, 1);
 }
 
 }  // namespace e3jb

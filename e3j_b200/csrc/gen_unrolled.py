@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Generates conv_unrolled_gen.inc: convolution kernels unrolled over the sparsity
+pattern of a Clebsch-Gordan table.
+
+    python e3j_b200/csrc/gen_unrolled.py
+
+For each variant (a pair of node / edge irreps with the l <= 3 output filter) the
+table of `e3j_b200.Convolution` gives the rows (i = output row, j = x row,
+k = y component, l = path).  Only that *pattern* is baked into the code; the
+coefficient values are read at run time (kernel parameters and a per-plan
+device table), so one variant serves every normalisation / avg_num_neighbors.
+
+Work decomposition (C = 128 channels, one lane owns 4 consecutive channels):
+
+forward   one CTA per receiver, NW warps; warp g owns the paths of group g (paths
+          grouped by the degree of their x irrep so every x row is fetched by one
+          warp only) and keeps their output rows in registers over the whole
+          edge segment.  Per edge a warp (a) copies the s and x rows it needs to
+          its private shared-memory stage with 16-byte async copies, one edge
+          ahead, each lane copying exactly the bytes it will read itself,
+          (b) forms each pair weight w[z,j] = sum_k val * y[k] in registers right
+          where it is used (values are kernel parameters, i.e. constant-bank
+          operands), (c) runs the unrolled multiply-adds
+          t[z] = sum_j w[z,j] x[j];  acc[z] += s[path] * t[z].
+backward  one CTA per receiver, NW warps; the receiver's cotangent rows dm[r] are
+          staged in shared memory once; each warp then takes whole edges
+          (e0 + warp, e0 + warp + NW, ...) and for each computes
+          v[j] = sum_z w[z,j] g[z];  ds[path] = sum_j x[j] v[j];
+          dx_msg[j] += s[path] v[j];  dy[k] += val * sum_c (s g[z]) x[j]
+          with the edge's rows arriving in chunks through a two-slot ring of
+          async copies, and reduces dy over the lanes with a halving butterfly.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import numpy as np  # noqa: E402
+
+from e3j_b200.convolution import Convolution  # noqa: E402
+
+VARIANTS = [
+    # id, name, x irreps, forward warps per receiver
+    (1, "l1l3", "0e+1o", 4),
+    (2, "l3l3", "0e+1o+2e+3o", 4),
+]
+Y_IRREPS = "0e+1o+2e+3o"
+OUT_FILTER = "0e+1o+2e+3o"
+BWD_WARPS = 4
+BWD_CHUNK_ROWS = 14  # rows (512 B each) per ring slot of the backward kernel
+
+
+class Path:
+    def __init__(self, p, rows):
+        self.p = p
+        self.nnz = rows  # list of (n, i, j, k)
+        self.zs = sorted({r[1] for r in rows})
+        self.js = sorted({r[2] for r in rows})
+        self.ks = sorted({r[3] for r in rows})
+        self.pairs = sorted({(r[1], r[2]) for r in rows})
+        self.cost_fwd = len(self.pairs) + len(self.zs)
+
+
+def analyse(x_irreps):
+    conv = Convolution((x_irreps, Y_IRREPS), OUT_FILTER, graph_ordering="RECEIVER")
+    idx = conv.coef.idx.astype(int)
+    order = np.lexsort((idx[:, 2], idx[:, 1], idx[:, 0]))
+    assert (order == np.arange(len(order))).all(), "table must be sorted by (i, j, k)"
+    S = conv.num_scalars
+    paths = []
+    for p in range(S):
+        rows = [(n, *idx[n, :3]) for n in range(len(idx)) if idx[n, 3] == p]
+        paths.append(Path(p, rows))
+    xsl = conv.source[0].slices()
+    for path in paths:
+        path.lx = next(n for n, s in enumerate(xsl) if s.start <= path.js[0] < s.stop)
+        sl = xsl[path.lx]
+        assert all(sl.start <= j < sl.stop for j in path.js)
+        path.xrows = list(range(sl.start, sl.stop))
+    return conv, idx, paths
+
+
+def group_paths(paths, nw):
+    """Groups by x irrep; the heaviest group is split until there are nw groups."""
+    groups = {}
+    for p in paths:
+        groups.setdefault(p.lx, []).append(p)
+    groups = [g for _, g in sorted(groups.items())]
+    cost = lambda g: sum(p.cost_fwd for p in g)  # noqa: E731
+    while len(groups) < nw:
+        groups.sort(key=cost)
+        heavy = groups.pop()
+        a, b = [], []
+        for p in sorted(heavy, key=lambda p: -p.cost_fwd):
+            (a if cost(a) <= cost(b) else b).append(p)
+        groups += [sorted(a, key=lambda p: p.p), sorted(b, key=lambda p: p.p)]
+    groups.sort(key=lambda g: (g[0].lx, g[0].p))
+    return groups
+
+
+class Emitter:
+    def __init__(self):
+        self.lines = []
+        self.ind = 0
+
+    def __call__(self, text=""):
+        for ln in text.split("\n"):
+            self.lines.append(("    " * self.ind + ln) if ln else "")
+
+    def block(self, head):
+        self(head + " {")
+        self.ind += 1
+
+    def end(self, tail="}"):
+        self.ind -= 1
+        self(tail)
+
+    def text(self):
+        return "\n".join(self.lines) + "\n"
+
+
+def weight_expr(path, z, j):
+    """w[z, j] = sum over the (at most two) table rows of the pair of val * y[k]."""
+    contrib = [(n, k) for (n, i, jj, k) in path.nnz if i == z and jj == j]
+    assert 1 <= len(contrib) <= 2
+    (n0, k0) = contrib[0]
+    expr = f"A.vals.v[{n0}] * y{k0}"
+    if len(contrib) == 2:
+        (n1, k1) = contrib[1]
+        expr = f"fmaf(A.vals.v[{n1}], y{k1}, {expr})"
+    return expr, contrib
+
+
+def emit_y_loads(em, ks):
+    """Loads the y components `ks` (broadcast float4 reads of the staged row)."""
+    for q in sorted({k // 4 for k in ks}):
+        em(f"const float4 yq{q} = ysm4[{q}];")
+    for k in sorted(ks):
+        em(f"const float y{k} = yq{k // 4}.{'xyzw'[k % 4]};")
+
+
+# ---------------------------------------------------------------------------
+# forward
+# ---------------------------------------------------------------------------
+def emit_fwd_group(em, vname, gi, group, dims):
+    X, Y, Z, S = dims
+    srows = [p.p for p in group]
+    xrows = sorted({j for p in group for j in p.xrows})
+    slot_s = {p: n for n, p in enumerate(srows)}
+    slot_x = {j: len(srows) + n for n, j in enumerate(xrows)}
+    nrows = len(srows) + len(xrows)
+    zs = [z for p in group for z in p.zs]
+    ks = sorted({k for p in group for k in p.ks})
+
+    em(f"// group {gi}: paths {srows}, x rows {xrows}, {len(zs)} output rows")
+    em(f"static constexpr int kFwdRows{gi} = {nrows};   // stage rows: s rows then x rows")
+    em.block(f"__device__ __forceinline__ void fwd_prefetch{gi}(const FwdArgs &A, int64_t e, int32_t a, float4 *stage, float *ysm, int lane)")
+    em("a = in_range(a, A.N) ? a : 0;")
+    em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
+    em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
+    em("float4 *dst = stage + lane;")
+    for p in srows:
+        em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * 128);")
+    for j in xrows:
+        em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
+    em(f"if (lane < 4) cp_async16_stream(ysm + lane * 4, A.y + e * {Y} + lane * 4);")
+    em.end()
+    em.block(f"__device__ __forceinline__ void fwd_group{gi}(const FwdArgs &A, float4 *stage, float *ysm, int lane)")
+    em(f"constexpr int kRows = kFwdRows{gi};")
+    em("float4 " + ", ".join(f"a{z}" for z in zs) + ";")
+    em.block("for (int64_t r = blockIdx.x; r < A.N; r += gridDim.x)")
+    em("const int32_t e0 = A.receiver_ptr[r], e1 = A.receiver_ptr[r + 1];")
+    em(" ".join(f"a{z} = make_float4(0.f, 0.f, 0.f, 0.f);" for z in zs))
+    em("int32_t snd_reg = -1;")
+    em.block("if (e0 < e1)")
+    em("snd_reg = (e0 + lane < e1) ? A.sender[e0 + lane] : -1;")
+    em(f"fwd_prefetch{gi}(A, e0, __shfl_sync(FULL, snd_reg, 0), stage, ysm, lane);")
+    em.end()
+    em("cp_async_commit();")
+    em.block("for (int32_t e = e0; e < e1; e++)")
+    em("const int rel = e - e0;")
+    em("const int st = rel & 1;")
+    em("const int32_t a = __shfl_sync(FULL, snd_reg, rel & 31);")
+    em("if (((rel + 1) & 31) == 0) snd_reg = (e + 1 + lane < e1) ? A.sender[e + 1 + lane] : -1;")
+    em("const int32_t a_next = __shfl_sync(FULL, snd_reg, (rel + 1) & 31);")
+    em(f"if (e + 1 < e1) fwd_prefetch{gi}(A, e + 1, a_next, stage + (st ^ 1) * kRows * 32, ysm + (st ^ 1) * 16, lane);")
+    em("cp_async_commit();")
+    em("cp_async_wait<1>();")
+    em("__syncwarp();")
+    em.block("if (in_range(a, A.N))")
+    em("const float4 *sg = stage + st * kRows * 32 + lane;")
+    em("const float4 *ysm4 = reinterpret_cast<const float4 *>(ysm + st * 16);")
+    emit_y_loads(em, ks)
+    cur_x = None
+    for path in group:
+        if cur_x != tuple(path.xrows):
+            if cur_x is not None:
+                em.end()
+            em.block("")
+            cur_x = tuple(path.xrows)
+            for j in path.xrows:
+                em(f"const float4 x{j} = sg[{slot_x[j]} * 32];")
+        em.block("")
+        em(f"const float4 sv = sg[{slot_s[path.p]} * 32];  // path {path.p}")
+        for z in path.zs:
+            js = [j for (zz, j) in path.pairs if zz == z]
+            em(f"{{ float4 t = mul_sv({weight_expr(path, z, js[0])[0]}, x{js[0]});")
+            for j in js[1:]:
+                em(f"  fma_sv(t, {weight_expr(path, z, j)[0]}, x{j});")
+            em(f"  fma_vv(a{z}, sv, t); }}")
+        em.end()
+    em.end()
+    em.end()  # valid edge
+    em("__syncwarp();")
+    em.end()  # edges
+    em("cp_async_wait<0>();")
+    em("__syncwarp();")
+    em(f"float4 *o = reinterpret_cast<float4 *>(A.out + (r * {Z}) * 128) + lane;")
+    for z in zs:
+        em(f"o[{z} * 32] = a{z};")
+    em.end()  # receivers
+    em.end()  # function
+    em()
+    return nrows
+
+
+# ---------------------------------------------------------------------------
+# backward
+# ---------------------------------------------------------------------------
+def make_chunks(paths):
+    """Chunks of paths (by x irrep) whose s rows + x rows fit one ring slot."""
+    by_lx = {}
+    for p in paths:
+        by_lx.setdefault(p.lx, []).append(p)
+    chunks, cur, rows = [], [], 0
+    for lx, grp in sorted(by_lx.items()):
+        need = len(grp) + len(grp[0].xrows)
+        if need > BWD_CHUNK_ROWS:
+            raise SystemExit(f"chunk for lx={lx} needs {need} rows")
+        if rows + need > BWD_CHUNK_ROWS and cur:
+            chunks.append(cur)
+            cur, rows = [], 0
+        cur.append((lx, grp))
+        rows += need
+    if cur:
+        chunks.append(cur)
+    return chunks
+
+
+def emit_bwd(em, vname, paths, dims):
+    X, Y, Z, S = dims
+    chunks = make_chunks(paths)
+    em(f"// backward: {len(chunks)} chunks per edge: " + "; ".join(
+        "+".join(f"lx{lx}({len(grp)} paths)" for lx, grp in ch) for ch in chunks))
+    em(f"static constexpr int kBwdChunks = {len(chunks)};")
+    em()
+    for ci, ch in enumerate(chunks):
+        srows = [p.p for _, grp in ch for p in grp]
+        xrows = [j for _, grp in ch for j in grp[0].xrows]
+        slot_s = {p: n for n, p in enumerate(srows)}
+        slot_x = {j: len(srows) + n for n, j in enumerate(xrows)}
+        ks = sorted({k for _, grp in ch for p in grp for k in p.ks})
+        em.block(f"__device__ __forceinline__ void bwd_prefetch{ci}(const BwdArgs &A, int64_t e, int32_t a, float4 *slot, int lane)")
+        em("a = in_range(a, A.N) ? a : 0;")
+        em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
+        em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
+        em("float4 *dst = slot + lane;")
+        for p in srows:
+            em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * 128);")
+        for j in xrows:
+            em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
+        em.end()
+        em.block(f"__device__ __forceinline__ void bwd_chunk{ci}(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float (&dyp)[16])")
+        em(f"float4 *ds_out = reinterpret_cast<float4 *>(A.ds + (e * {S}) * 128) + lane;")
+        em(f"float4 *dx_out = reinterpret_cast<float4 *>(A.dxm + (e * {X}) * 128) + lane;")
+        em("const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);")
+        em.block("if (!valid)")
+        for p in srows:
+            em(f"st_stream4(ds_out + {p} * 32, zero4);")
+        for j in xrows:
+            em(f"st_stream4(dx_out + {j} * 32, zero4);")
+        em("return;")
+        em.end()
+        em("const float4 *ysm4 = reinterpret_cast<const float4 *>(ysm);")
+        emit_y_loads(em, ks)
+        for lx, grp in ch:
+            em.block("")
+            for j in grp[0].xrows:
+                em(f"const float4 x{j} = sg[{slot_x[j]} * 32];")
+            em("float4 " + ", ".join(f"dx{j} = zero4" for j in grp[0].xrows) + ";")
+            for path in grp:
+                em.block("")
+                em(f"const float4 sv = sg[{slot_s[path.p]} * 32];  // path {path.p}")
+                em("float4 " + ", ".join(f"v{j} = zero4" for j in path.js) + ";")
+                for z in path.zs:
+                    em(f"{{ const float4 g = gsm[{z} * 32]; const float4 gs = mul_vv(sv, g);")
+                    for (zz, j) in path.pairs:
+                        if zz != z:
+                            continue
+                        expr, contrib = weight_expr(path, z, j)
+                        em(f"  fma_sv(v{j}, {expr}, g);")
+                        em(f"  {{ const float d = dot4(gs, x{j}); " + " ".join(
+                            f"dyp[{k}] = fmaf(A.vals.v[{n}], d, dyp[{k}]);" for n, k in contrib) + " }")
+                    em("}")
+                js = path.js
+                em(f"{{ float4 dsv = mul_vv(x{js[0]}, v{js[0]});")
+                for j in js[1:]:
+                    em(f"  fma_vv(dsv, x{j}, v{j});")
+                em(f"  st_stream4(ds_out + {path.p} * 32, dsv); }}")
+                for j in js:
+                    em(f"fma_vv(dx{j}, sv, v{j});")
+                em.end()
+            for j in grp[0].xrows:
+                em(f"st_stream4(dx_out + {j} * 32, dx{j});")
+            em.end()
+        em.end()
+        em()
+    return chunks
+
+
+def emit_variant(em, vid, name, x_irreps, nw):
+    conv, idx, paths = analyse(x_irreps)
+    X, Y, Z, S = conv.source[0].dim, conv.source[1].dim, conv.target.dim, conv.num_scalars
+    nnz = len(idx)
+    em(f"// ===== variant {vid} ({name}): x = {x_irreps}, y = {Y_IRREPS}, filter {OUT_FILTER} =====")
+    em(f"namespace {name} {{")
+    em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz}, NW = {nw};")
+    em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
+    em("struct Vals { float v[NNZ]; };")
+    em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N; Vals vals; };")
+    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N; Vals vals; };")
+    em()
+    groups = group_paths(paths, nw)
+    rows = [emit_fwd_group(em, name, gi, g, (X, Y, Z, S)) for gi, g in enumerate(groups)]
+    em(f"static constexpr int kFwdMaxRows = {max(rows)};")
+    em.block("__device__ __forceinline__ void fwd_dispatch(int group, const FwdArgs &A, float4 *stage, float *ysm, int lane)")
+    em.block("switch (group)")
+    for gi in range(len(groups)):
+        em(f"case {gi}: fwd_group{gi}(A, stage, ysm, lane); break;")
+    em.end()
+    em.end()
+    em()
+    chunks = emit_bwd(em, name, paths, (X, Y, Z, S))
+    em.block("__device__ __forceinline__ void bwd_prefetch_step(int c, const BwdArgs &A, int64_t e, int32_t a, float4 *slot, float *ysm, int lane)")
+    em.block("switch (c)")
+    for ci in range(len(chunks)):
+        em(f"case {ci}: bwd_prefetch{ci}(A, e, a, slot, lane); break;")
+    em.end()
+    em(f"if (c == 0 && lane < 4) cp_async16_stream(ysm + lane * 4, A.y + e * {Y} + lane * 4);")
+    em.end()
+    em.block("__device__ __forceinline__ void bwd_compute_step(int c, const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float (&dyp)[16])")
+    em.block("switch (c)")
+    for ci in range(len(chunks)):
+        em(f"case {ci}: bwd_chunk{ci}(A, sg, gsm, ysm, e, valid, lane, dyp); break;")
+    em.end()
+    em.end()
+    em("#include \"conv_unrolled_kernels.inc\"")
+    em(f"}}  // namespace {name}")
+    em()
+    return dict(id=vid, name=name, X=X, Y=Y, Z=Z, S=S, nnz=nnz, nw=nw, fwd_rows=max(rows), chunks=len(chunks))
+
+
+def main():
+    em = Emitter()
+    em("// GENERATED by gen_unrolled.py — do not edit; regenerate instead.")
+    em("// clang-format off")
+    infos = [emit_variant(em, *v) for v in VARIANTS]
+    out = os.path.join(HERE, "conv_unrolled_gen.inc")
+    with open(out, "w") as fh:
+        fh.write(em.text())
+    print("wrote", out, len(em.lines), "lines", infos)
+
+
+if __name__ == "__main__":
+    main()

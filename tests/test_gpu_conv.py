@@ -203,13 +203,19 @@ def test_node_mask_and_avg_num_neighbors():
     a = conv1(x, y, s, dev(snd), dev(rcv))
     b = conv4(x, y, s, dev(snd), dev(rcv))
     assert torch.allclose(a, 4 * b, rtol=1e-6, atol=1e-6)
+    # trailing padding nodes: padding edges connect padding nodes only and lie at the end
+    # (the contract of GraphCSR.mask_edges, src/e3j/data/graph.py:76-91)
+    real = n - 2
+    snd2 = np.concatenate([rng.integers(0, real, e - 4), [real, real + 1, real, real + 1]]).astype(np.int32)
+    rcv2 = np.concatenate([np.sort(rng.integers(0, real, e - 4)), [real, real, real + 1, real + 1]]).astype(np.int32)
     mask = torch.ones(n, dtype=torch.bool, device=DEV)
-    mask[-2:] = False
-    m = conv1(x, y, s, dev(snd), dev(rcv), node_mask=mask)
-    keep = (snd < n - 2) & (rcv < n - 2)
+    mask[real:] = False
+    m = conv1(x, y, s, dev(snd2), dev(rcv2), node_mask=mask)
+    keep = (snd2 < real) & (rcv2 < real)
     want = numpy_oracle.conv_fwd(conv1.coef.val, conv1.coef.idx, x.cpu().numpy(), y.cpu().numpy()[keep],
-                                 s.cpu().numpy()[keep], snd[keep], rcv[keep], conv1.target.dim)  # fmt: skip
+                                 s.cpu().numpy()[keep], snd2[keep], rcv2[keep], conv1.target.dim)  # fmt: skip
     assert_close(m.cpu().numpy(), want)
+    assert (m[real:] == 0).all()
 
 
 def test_double_backward_matches_oracle_composition():
