@@ -199,7 +199,7 @@ def run_ours(args):
     cfg = args.config
     conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
                        avg_num_neighbors=30.0)  # fmt: skip
-    g = problems.make_graph(cfg, seed=rank)
+    g = problems.make_graph(cfg, seed=rank, num_nodes=args.nodes)
     x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
     X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
     plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
@@ -349,6 +349,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--nodes", type=int, default=None, help="override the node count (small profiling cases)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

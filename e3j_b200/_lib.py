@@ -14,7 +14,8 @@ import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-LIB_PATH = os.path.join(_HERE, "libe3j_b200.so")
+# E3J_B200_LIB points at an alternative build of the same sources (tuning experiments)
+LIB_PATH = os.environ.get("E3J_B200_LIB") or os.path.join(_HERE, "libe3j_b200.so")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 
 # fast math stays off: results are held to fp32 tolerances

@@ -170,15 +170,24 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
     }
 }
 
-// Edges at or beyond receiver_ptr[N] belong to no receiver: exact zeros
+// Finishes the per-edge pass: (a) when that pass left `nparts` > 1 partial dy buffers
+// (E * dy_row floats each), dy = their sum in buffer order; (b) edges at or beyond
+// receiver_ptr[N] belong to no receiver: their dy, ds and dx message are exact zeros
 // (lib/e3j_ops/cuda/convolution/bwd.cuh:308-319).
-__global__ void zero_tail_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t E,
-                                 float *__restrict__ dxm, int64_t dxm_row, float *__restrict__ dy,
-                                 int64_t dy_row, float *__restrict__ ds, int64_t ds_row) {
-    const int64_t first = receiver_ptr[N];
+__global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t E,
+                                  float *__restrict__ dxm, int64_t dxm_row, float *__restrict__ dy,
+                                  int64_t dy_row, float *__restrict__ ds, int64_t ds_row,
+                                  const float *__restrict__ dy_part, int nparts) {
+    const int64_t first = min((int64_t)receiver_ptr[N], E);
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    if (first >= E) return;
+    if (nparts > 1) {
+        for (int64_t t = tid; t < first * dy_row; t += step) {
+            float v = dy_part[t];
+            for (int p = 1; p < nparts; p++) v += dy_part[(int64_t)p * E * dy_row + t];
+            dy[t] = v;
+        }
+    }
     for (int64_t t = first * dxm_row + tid; t < E * dxm_row; t += step) dxm[t] = 0.f;
     for (int64_t t = first * dy_row + tid; t < E * dy_row; t += step) dy[t] = 0.f;
     for (int64_t t = first * ds_row + tid; t < E * ds_row; t += step) ds[t] = 0.f;

@@ -234,7 +234,9 @@ int e3j_b200_conv_fwd(const e3j_b200_plan *p, const float *x, const float *y, co
 size_t e3j_b200_conv_bwd_workspace_bytes(const e3j_b200_plan *p, int32_t N, int64_t E) {
     (void)N;
     if (!p || E <= 0) return 256;
-    return ((size_t)E * p->d.X * p->d.C * sizeof(float) + 255) / 256 * 256;
+    const size_t dxm = ((size_t)E * p->d.X * p->d.C * sizeof(float) + 255) / 256 * 256;
+    const size_t parts = p->un.dy_partials > 1 ? (size_t)p->un.dy_partials * E * p->d.Y * sizeof(float) : 0;
+    return dxm + (parts + 255) / 256 * 256;
 }
 
 int e3j_b200_conv_bwd(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
@@ -265,11 +267,15 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
         return set_error(E3J_B200_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
     float *dxm = static_cast<float *>(workspace);
     const Dims &d = p->d;
+    const int nparts = p->variant != E3J_B200_VARIANT_GENERIC ? p->un.dy_partials : 1;
+    float *dy_part = nparts > 1 ? reinterpret_cast<float *>(static_cast<char *>(workspace) +
+                                                            ((size_t)E * d.X * d.C * sizeof(float) + 255) / 256 * 256)
+                                : dy;
 
     if (E > 0 && (phases & E3J_B200_BWD_EDGES)) {
         if (p->variant != E3J_B200_VARIANT_GENERIC) {
             rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y, s, dm, sender,
-                                            receiver_ptr, dxm, dy, ds, N, E, debug, stream);
+                                            receiver_ptr, dxm, dy_part, ds, N, E, debug, stream);
             if (rc) return rc;
         } else {
             const GenericGeometry g = generic_geometry(p);
@@ -292,8 +298,8 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
         }
     }
     if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
-        generic::zero_tail_kernel<<<p->lim.sm_count, 256, 0, stream>>>(
-            receiver_ptr, N, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C);
+        generic::bwd_finish_kernel<<<p->lim.sm_count * 4, 256, 0, stream>>>(
+            receiver_ptr, N, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
         rc = check_launch("convolution_bwd (tail)", debug, stream);
         if (rc) return rc;
     }

@@ -44,14 +44,19 @@ import numpy as np  # noqa: E402
 from e3j_b200.convolution import Convolution  # noqa: E402
 
 VARIANTS = [
-    # id, name, x irreps, forward warps per receiver
-    (1, "l1l3", "0e+1o", 4),
-    (2, "l3l3", "0e+1o+2e+3o", 4),
+    # forward: nw warps per receiver (path groups), rpc receivers per CTA, nst stages per warp,
+    #          fmin = CTAs per SM the register budget is set for
+    # backward: bw warps per CTA, nslot ring slots per warp, slot_rows rows per slot, bmin as fmin
+    # fwd_groups: explicit path groups (else derived); rot = 1 rotates the group -> warp map per CTA
+    # fsplit / bsplit = 1 launches one kernel per forward group / backward chunk, so that each
+    # kernel's loop stays small enough for the instruction cache
+    dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, bw=4, nslot=3, slot_rows=14,
+         bmin=2, bsplit=0, fwd_groups=None),
+    dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, bw=4, nslot=3, slot_rows=14,
+         bmin=2, bsplit=1, fwd_groups=None),
 ]
 Y_IRREPS = "0e+1o+2e+3o"
 OUT_FILTER = "0e+1o+2e+3o"
-BWD_WARPS = 4
-BWD_CHUNK_ROWS = 14  # rows (512 B each) per ring slot of the backward kernel
 
 
 class Path:
@@ -85,19 +90,34 @@ def analyse(x_irreps):
 
 
 def group_paths(paths, nw):
-    """Groups by x irrep; the heaviest group is split until there are nw groups."""
+    """Path groups of the forward kernel, one per warp of a receiver.  Starts from
+    the x irreps (so an x row is fetched by one warp); the lightest groups are
+    merged while there are more than nw, the heaviest is split while fewer."""
     groups = {}
     for p in paths:
         groups.setdefault(p.lx, []).append(p)
     groups = [g for _, g in sorted(groups.items())]
     cost = lambda g: sum(p.cost_fwd for p in g)  # noqa: E731
+    while len(groups) > nw:
+        groups.sort(key=cost)
+        a, b = groups.pop(0), groups.pop(0)
+        groups.append(sorted(a + b, key=lambda p: (p.lx, p.p)))
     while len(groups) < nw:
         groups.sort(key=cost)
         heavy = groups.pop()
         a, b = [], []
         for p in sorted(heavy, key=lambda p: -p.cost_fwd):
             (a if cost(a) <= cost(b) else b).append(p)
-        groups += [sorted(a, key=lambda p: p.p), sorted(b, key=lambda p: p.p)]
+        groups += [sorted(a, key=lambda p: (p.lx, p.p)), sorted(b, key=lambda p: (p.lx, p.p))]
+    if nw == 2 and len({p.lx for p in paths}) == 2:
+        # two x irreps of very different cost: move paths from the heavy group to the light one
+        groups.sort(key=cost)
+        light, heavy = groups
+        for p in sorted(heavy, key=lambda p: -p.cost_fwd):
+            if cost(light) + p.cost_fwd <= cost(heavy) - p.cost_fwd + p.cost_fwd // 2:
+                heavy.remove(p)
+                light.append(p)
+        groups = [sorted(light, key=lambda p: (p.lx, p.p)), sorted(heavy, key=lambda p: (p.lx, p.p))]
     groups.sort(key=lambda g: (g[0].lx, g[0].p))
     return groups
 
@@ -128,10 +148,10 @@ def weight_expr(path, z, j):
     contrib = [(n, k) for (n, i, jj, k) in path.nnz if i == z and jj == j]
     assert 1 <= len(contrib) <= 2
     (n0, k0) = contrib[0]
-    expr = f"A.vals.v[{n0}] * y{k0}"
+    expr = f"__fmul2_rn(A.vals.v[{n0}], y{k0})"
     if len(contrib) == 2:
         (n1, k1) = contrib[1]
-        expr = f"fmaf(A.vals.v[{n1}], y{k1}, {expr})"
+        expr = f"__ffma2_rn(A.vals.v[{n1}], y{k1}, {expr})"
     return expr, contrib
 
 
@@ -140,7 +160,7 @@ def emit_y_loads(em, ks):
     for q in sorted({k // 4 for k in ks}):
         em(f"const float4 yq{q} = ysm4[{q}];")
     for k in sorted(ks):
-        em(f"const float y{k} = yq{k // 4}.{'xyzw'[k % 4]};")
+        em(f"const float2 y{k} = dup2(yq{k // 4}.{'xyzw'[k % 4]});")
 
 
 # ---------------------------------------------------------------------------
@@ -155,10 +175,17 @@ def emit_fwd_group(em, vname, gi, group, dims):
     nrows = len(srows) + len(xrows)
     zs = [z for p in group for z in p.zs]
     ks = sorted({k for p in group for k in p.ks})
+    cost = sum(p.cost_fwd for p in group)
 
-    em(f"// group {gi}: paths {srows}, x rows {xrows}, {len(zs)} output rows")
-    em(f"static constexpr int kFwdRows{gi} = {nrows};   // stage rows: s rows then x rows")
-    em.block(f"__device__ __forceinline__ void fwd_prefetch{gi}(const FwdArgs &A, int64_t e, int32_t a, float4 *stage, float *ysm, int lane)")
+    em(f"// forward group {gi}: paths {srows}, x rows {xrows}, {len(zs)} output rows, cost {cost}")
+    em(f"struct FwdG{gi} {{")
+    em.ind += 1
+    em(f"static constexpr int kRows = {nrows};   // stage rows: s rows then x rows")
+    em("struct Acc { f4 " + ", ".join(f"a{z}" for z in zs) + "; };")
+    em.block("static __device__ __forceinline__ void zero(Acc &c)")
+    em(" ".join(f"c.a{z} = zero_f4();" for z in zs))
+    em.end()
+    em.block("static __device__ __forceinline__ void prefetch(const FwdArgs &A, int64_t e, int32_t a, float4 *stage, float *ysm, int lane)")
     em("a = in_range(a, A.N) ? a : 0;")
     em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
     em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
@@ -169,31 +196,8 @@ def emit_fwd_group(em, vname, gi, group, dims):
         em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
     em(f"if (lane < 4) cp_async16_stream(ysm + lane * 4, A.y + e * {Y} + lane * 4);")
     em.end()
-    em.block(f"__device__ __forceinline__ void fwd_group{gi}(const FwdArgs &A, float4 *stage, float *ysm, int lane)")
-    em(f"constexpr int kRows = kFwdRows{gi};")
-    em("float4 " + ", ".join(f"a{z}" for z in zs) + ";")
-    em.block("for (int64_t r = blockIdx.x; r < A.N; r += gridDim.x)")
-    em("const int32_t e0 = A.receiver_ptr[r], e1 = A.receiver_ptr[r + 1];")
-    em(" ".join(f"a{z} = make_float4(0.f, 0.f, 0.f, 0.f);" for z in zs))
-    em("int32_t snd_reg = -1;")
-    em.block("if (e0 < e1)")
-    em("snd_reg = (e0 + lane < e1) ? A.sender[e0 + lane] : -1;")
-    em(f"fwd_prefetch{gi}(A, e0, __shfl_sync(FULL, snd_reg, 0), stage, ysm, lane);")
-    em.end()
-    em("cp_async_commit();")
-    em.block("for (int32_t e = e0; e < e1; e++)")
-    em("const int rel = e - e0;")
-    em("const int st = rel & 1;")
-    em("const int32_t a = __shfl_sync(FULL, snd_reg, rel & 31);")
-    em("if (((rel + 1) & 31) == 0) snd_reg = (e + 1 + lane < e1) ? A.sender[e + 1 + lane] : -1;")
-    em("const int32_t a_next = __shfl_sync(FULL, snd_reg, (rel + 1) & 31);")
-    em(f"if (e + 1 < e1) fwd_prefetch{gi}(A, e + 1, a_next, stage + (st ^ 1) * kRows * 32, ysm + (st ^ 1) * 16, lane);")
-    em("cp_async_commit();")
-    em("cp_async_wait<1>();")
-    em("__syncwarp();")
-    em.block("if (in_range(a, A.N))")
-    em("const float4 *sg = stage + st * kRows * 32 + lane;")
-    em("const float4 *ysm4 = reinterpret_cast<const float4 *>(ysm + st * 16);")
+    em.block("static __device__ __forceinline__ void compute(const FwdArgs &A, Acc &c, const float4 *sg, const float *ysm)")
+    em("const float4 *ysm4 = reinterpret_cast<const float4 *>(ysm);")
     emit_y_loads(em, ks)
     cur_x = None
     for path in group:
@@ -203,27 +207,27 @@ def emit_fwd_group(em, vname, gi, group, dims):
             em.block("")
             cur_x = tuple(path.xrows)
             for j in path.xrows:
-                em(f"const float4 x{j} = sg[{slot_x[j]} * 32];")
+                em(f"const f4 x{j} = ld4(sg + {slot_x[j]} * 32);")
         em.block("")
-        em(f"const float4 sv = sg[{slot_s[path.p]} * 32];  // path {path.p}")
+        em(f"const f4 sv = ld4(sg + {slot_s[path.p]} * 32);  // path {path.p}")
         for z in path.zs:
             js = [j for (zz, j) in path.pairs if zz == z]
-            em(f"{{ float4 t = mul_sv({weight_expr(path, z, js[0])[0]}, x{js[0]});")
+            em(f"{{ f4 t = mul_sv({weight_expr(path, z, js[0])[0]}, x{js[0]});")
             for j in js[1:]:
                 em(f"  fma_sv(t, {weight_expr(path, z, j)[0]}, x{j});")
-            em(f"  fma_vv(a{z}, sv, t); }}")
+            em(f"  fma_vv(c.a{z}, sv, t); }}")
         em.end()
     em.end()
-    em.end()  # valid edge
-    em("__syncwarp();")
-    em.end()  # edges
-    em("cp_async_wait<0>();")
-    em("__syncwarp();")
-    em(f"float4 *o = reinterpret_cast<float4 *>(A.out + (r * {Z}) * 128) + lane;")
+    em.end()  # compute
+    em.block("static __device__ __forceinline__ void store(const Acc &c, float4 *o)")
     for z in zs:
-        em(f"o[{z} * 32] = a{z};")
-    em.end()  # receivers
-    em.end()  # function
+        em(f"o[{z} * 32] = as_float4(c.a{z});")
+    em.end()
+    em.block("static __device__ __forceinline__ void store_zero(float4 *o, const float4 &zero4)")
+    for z in zs:
+        em(f"o[{z} * 32] = zero4;")
+    em.end()
+    em.end("};")
     em()
     return nrows
 
@@ -231,7 +235,7 @@ def emit_fwd_group(em, vname, gi, group, dims):
 # ---------------------------------------------------------------------------
 # backward
 # ---------------------------------------------------------------------------
-def make_chunks(paths):
+def make_chunks(paths, slot_rows):
     """Chunks of paths (by x irrep) whose s rows + x rows fit one ring slot."""
     by_lx = {}
     for p in paths:
@@ -239,9 +243,9 @@ def make_chunks(paths):
     chunks, cur, rows = [], [], 0
     for lx, grp in sorted(by_lx.items()):
         need = len(grp) + len(grp[0].xrows)
-        if need > BWD_CHUNK_ROWS:
+        if need > slot_rows:
             raise SystemExit(f"chunk for lx={lx} needs {need} rows")
-        if rows + need > BWD_CHUNK_ROWS and cur:
+        if rows + need > slot_rows and cur:
             chunks.append(cur)
             cur, rows = [], 0
         cur.append((lx, grp))
@@ -251,20 +255,28 @@ def make_chunks(paths):
     return chunks
 
 
-def emit_bwd(em, vname, paths, dims):
+def emit_bwd(em, vname, paths, dims, slot_rows):
     X, Y, Z, S = dims
-    chunks = make_chunks(paths)
+    chunks = make_chunks(paths, slot_rows)
     em(f"// backward: {len(chunks)} chunks per edge: " + "; ".join(
         "+".join(f"lx{lx}({len(grp)} paths)" for lx, grp in ch) for ch in chunks))
     em(f"static constexpr int kBwdChunks = {len(chunks)};")
     em()
+    g_base, g_rows_all = 0, []
     for ci, ch in enumerate(chunks):
         srows = [p.p for _, grp in ch for p in grp]
         xrows = [j for _, grp in ch for j in grp[0].xrows]
         slot_s = {p: n for n, p in enumerate(srows)}
         slot_x = {j: len(srows) + n for n, j in enumerate(xrows)}
         ks = sorted({k for _, grp in ch for p in grp for k in p.ks})
-        em.block(f"__device__ __forceinline__ void bwd_prefetch{ci}(const BwdArgs &A, int64_t e, int32_t a, float4 *slot, int lane)")
+        zrows = [z for _, grp in ch for p in grp for z in p.zs]
+        gslot = {z: g_base + n for n, z in enumerate(zrows)}
+        g_rows_all.extend(zrows)
+        em(f"struct BwdC{ci} {{")
+        em.ind += 1
+        em(f"static constexpr int kRows = {len(srows) + len(xrows)};")
+        em(f"static constexpr int kGBase = {g_base}, kGRows = {len(zrows)};  // rows of the staged dm block it reads")
+        em.block("static __device__ __forceinline__ void prefetch(const BwdArgs &A, int64_t e, int32_t a, float4 *slot, int lane)")
         em("a = in_range(a, A.N) ? a : 0;")
         em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
         em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
@@ -274,10 +286,10 @@ def emit_bwd(em, vname, paths, dims):
         for j in xrows:
             em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
         em.end()
-        em.block(f"__device__ __forceinline__ void bwd_chunk{ci}(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float (&dyp)[16])")
+        em.block("static __device__ __forceinline__ void compute(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float2 (&dyp)[16])")
         em(f"float4 *ds_out = reinterpret_cast<float4 *>(A.ds + (e * {S}) * 128) + lane;")
         em(f"float4 *dx_out = reinterpret_cast<float4 *>(A.dxm + (e * {X}) * 128) + lane;")
-        em("const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);")
+        em("const f4 zero4 = zero_f4();")
         em.block("if (!valid)")
         for p in srows:
             em(f"st_stream4(ds_out + {p} * 32, zero4);")
@@ -290,24 +302,24 @@ def emit_bwd(em, vname, paths, dims):
         for lx, grp in ch:
             em.block("")
             for j in grp[0].xrows:
-                em(f"const float4 x{j} = sg[{slot_x[j]} * 32];")
-            em("float4 " + ", ".join(f"dx{j} = zero4" for j in grp[0].xrows) + ";")
+                em(f"const f4 x{j} = ld4(sg + {slot_x[j]} * 32);")
+            em("f4 " + ", ".join(f"dx{j} = zero4" for j in grp[0].xrows) + ";")
             for path in grp:
                 em.block("")
-                em(f"const float4 sv = sg[{slot_s[path.p]} * 32];  // path {path.p}")
-                em("float4 " + ", ".join(f"v{j} = zero4" for j in path.js) + ";")
+                em(f"const f4 sv = ld4(sg + {slot_s[path.p]} * 32);  // path {path.p}")
+                em("f4 " + ", ".join(f"v{j} = zero4" for j in path.js) + ";")
                 for z in path.zs:
-                    em(f"{{ const float4 g = gsm[{z} * 32]; const float4 gs = mul_vv(sv, g);")
+                    em(f"{{ const f4 g = ld4(gsm + {gslot[z]} * 32); const f4 gs = mul_vv(sv, g);")
                     for (zz, j) in path.pairs:
                         if zz != z:
                             continue
                         expr, contrib = weight_expr(path, z, j)
                         em(f"  fma_sv(v{j}, {expr}, g);")
-                        em(f"  {{ const float d = dot4(gs, x{j}); " + " ".join(
-                            f"dyp[{k}] = fmaf(A.vals.v[{n}], d, dyp[{k}]);" for n, k in contrib) + " }")
+                        em(f"  {{ const float2 d = dot_halves(gs, x{j}); " + " ".join(
+                            f"dyp[{k}] = __ffma2_rn(A.vals.v[{n}], d, dyp[{k}]);" for n, k in contrib) + " }")
                     em("}")
                 js = path.js
-                em(f"{{ float4 dsv = mul_vv(x{js[0]}, v{js[0]});")
+                em(f"{{ f4 dsv = mul_vv(x{js[0]}, v{js[0]});")
                 for j in js[1:]:
                     em(f"  fma_vv(dsv, x{j}, v{j});")
                 em(f"  st_stream4(ds_out + {path.p} * 32, dsv); }}")
@@ -318,61 +330,86 @@ def emit_bwd(em, vname, paths, dims):
                 em(f"st_stream4(dx_out + {j} * 32, dx{j});")
             em.end()
         em.end()
+        em.end("};")
         em()
+        g_base += len(zrows)
+    em("// output rows in the order they are staged in shared memory (chunk after chunk)")
+    em(f"static __device__ const int16_t g_row_of_slot[{len(g_rows_all)}] = {{{', '.join(map(str, g_rows_all))}}};")
     return chunks
 
 
-def emit_variant(em, vid, name, x_irreps, nw):
+def emit_variant(em, v):
+    vid, name, x_irreps, nw = v["id"], v["name"], v["x"], v["nw"]
     conv, idx, paths = analyse(x_irreps)
     X, Y, Z, S = conv.source[0].dim, conv.source[1].dim, conv.target.dim, conv.num_scalars
     nnz = len(idx)
     em(f"// ===== variant {vid} ({name}): x = {x_irreps}, y = {Y_IRREPS}, filter {OUT_FILTER} =====")
     em(f"namespace {name} {{")
-    em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz}, NW = {nw};")
+    em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz};")
+    em(f"static constexpr int NW = {nw}, RPC = {v['rpc']}, NST = {v['nst']}, kFwdMinCtas = {v['fmin']}, kFwdRotate = {v['rot']}, kFwdSplit = {v['fsplit']};")
+    em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
-    em("struct Vals { float v[NNZ]; };")
-    em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N; Vals vals; };")
-    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N; Vals vals; };")
+    em("struct Vals { float2 v[NNZ]; };  // each value duplicated: operand of packed multiplies")
+    em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N; int64_t E; Vals vals; };")
+    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N; int64_t E; Vals vals; };")
     em()
-    groups = group_paths(paths, nw)
+    if v.get("fwd_groups"):
+        groups = [sorted((paths[p] for p in g), key=lambda p: (p.lx, p.p)) for g in v["fwd_groups"]]
+        assert sorted(p.p for g in groups for p in g) == list(range(S)) and len(groups) == nw
+    else:
+        groups = group_paths(paths, nw)
     rows = [emit_fwd_group(em, name, gi, g, (X, Y, Z, S)) for gi, g in enumerate(groups)]
     em(f"static constexpr int kFwdMaxRows = {max(rows)};")
-    em.block("__device__ __forceinline__ void fwd_dispatch(int group, const FwdArgs &A, float4 *stage, float *ysm, int lane)")
+    chunks = emit_bwd(em, name, paths, (X, Y, Z, S), v["slot_rows"])
+    em("#include \"conv_unrolled_kernels.inc\"")
+    em.block("__device__ __forceinline__ void fwd_dispatch(int group, const FwdArgs &A, int64_t r0, int64_t r1, float4 *stage, float *meta, int lane)")
     em.block("switch (group)")
     for gi in range(len(groups)):
-        em(f"case {gi}: fwd_group{gi}(A, stage, ysm, lane); break;")
+        em(f"case {gi}: fwd_run<FwdG{gi}>(A, r0, r1, stage, meta, lane); break;")
     em.end()
     em.end()
-    em()
-    chunks = emit_bwd(em, name, paths, (X, Y, Z, S))
+    em("template <int C> struct BwdChunkSel;")
+    em("template <> struct BwdChunkSel<-1> { static constexpr int kGBase = 0, kGRows = Z; };  // all chunks")
+    for ci in range(len(chunks)):
+        em(f"template <> struct BwdChunkSel<{ci}> : BwdC{ci} {{}};")
+    em("template <int G> struct FwdGroupSel;")
+    for gi in range(len(groups)):
+        em(f"template <> struct FwdGroupSel<{gi}> {{ using type = FwdG{gi}; }};")
     em.block("__device__ __forceinline__ void bwd_prefetch_step(int c, const BwdArgs &A, int64_t e, int32_t a, float4 *slot, float *ysm, int lane)")
     em.block("switch (c)")
     for ci in range(len(chunks)):
-        em(f"case {ci}: bwd_prefetch{ci}(A, e, a, slot, lane); break;")
+        em(f"case {ci}: BwdC{ci}::prefetch(A, e, a, slot, lane); break;")
     em.end()
-    em(f"if (c == 0 && lane < 4) cp_async16_stream(ysm + lane * 4, A.y + e * {Y} + lane * 4);")
     em.end()
-    em.block("__device__ __forceinline__ void bwd_compute_step(int c, const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float (&dyp)[16])")
+    em.block("__device__ __forceinline__ void bwd_compute_step(int c, const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float2 (&dyp)[16])")
     em.block("switch (c)")
     for ci in range(len(chunks)):
-        em(f"case {ci}: bwd_chunk{ci}(A, sg, gsm, ysm, e, valid, lane, dyp); break;")
+        em(f"case {ci}: BwdC{ci}::compute(A, sg, gsm, ysm, e, valid, lane, dyp); break;")
     em.end()
     em.end()
-    em("#include \"conv_unrolled_kernels.inc\"")
+    em("#include \"conv_unrolled_entry.inc\"")
     em(f"}}  // namespace {name}")
     em()
-    return dict(id=vid, name=name, X=X, Y=Y, Z=Z, S=S, nnz=nnz, nw=nw, fwd_rows=max(rows), chunks=len(chunks))
+    return dict(id=vid, name=name, X=X, Y=Y, Z=Z, S=S, nnz=nnz, groups=[[p.p for p in g] for g in groups],
+                group_cost=[sum(p.cost_fwd for p in g) for g in groups], fwd_rows=rows, chunks=len(chunks))
 
 
 def main():
+    # tuning hook: JSON {variant name: {parameter: value}} overriding VARIANTS for one run
+    import json
+
+    for name, upd in json.loads(os.environ.get("E3J_B200_GEN_OVERRIDES", "{}")).items():
+        next(v for v in VARIANTS if v["name"] == name).update(upd)
     em = Emitter()
     em("// GENERATED by gen_unrolled.py — do not edit; regenerate instead.")
     em("// clang-format off")
-    infos = [emit_variant(em, *v) for v in VARIANTS]
-    out = os.path.join(HERE, "conv_unrolled_gen.inc")
+    infos = [emit_variant(em, v) for v in VARIANTS]
+    out = os.environ.get("E3J_B200_GEN_OUT") or os.path.join(HERE, "conv_unrolled_gen.inc")
     with open(out, "w") as fh:
         fh.write(em.text())
-    print("wrote", out, len(em.lines), "lines", infos)
+    print("wrote", out, len(em.lines), "lines")
+    for i in infos:
+        print(i)
 
 
 if __name__ == "__main__":

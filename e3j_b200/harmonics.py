@@ -187,7 +187,7 @@ class Harmonics:
         terms = terms * self.mono_coef.astype(u.dtype)[:, None]
         out = np.zeros((self.dim, u.shape[0]), dtype=u.dtype)
         np.add.at(out, self.mono_row, terms)
-        return out.T
+        return np.ascontiguousarray(out.T)
 
     def __call__(self, r: np.ndarray) -> np.ndarray:
         r = np.asarray(r)

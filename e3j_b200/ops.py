@@ -142,6 +142,8 @@ def _stream() -> ctypes.c_void_p:
 def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     dev = tensors[0].device
     for t in tensors:
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous (row-major, channel axis last)")
         if t.device.type != "cuda":
             raise RuntimeError(
                 "e3j_b200 operators run on CUDA devices only (tensor on "
