@@ -50,9 +50,10 @@ VARIANTS = [
     # fwd_groups: explicit path groups (else derived); rot = 1 rotates the group -> warp map per CTA
     # fsplit / bsplit = 1 launches one kernel per forward group / backward chunk, so that each
     # kernel's loop stays small enough for the instruction cache
-    dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, bw=4, nslot=3, slot_rows=14,
+    # fw = warps per CTA of a split forward kernel
+    dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, fw=4, bw=4, nslot=3, slot_rows=14,
          bmin=2, bsplit=0, fwd_groups=None),
-    dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, bw=4, nslot=3, slot_rows=14,
+    dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=3, slot_rows=14,
          bmin=2, bsplit=1, fwd_groups=None),
 ]
 Y_IRREPS = "0e+1o+2e+3o"
@@ -148,11 +149,11 @@ def weight_expr(path, z, j):
     contrib = [(n, k) for (n, i, jj, k) in path.nnz if i == z and jj == j]
     assert 1 <= len(contrib) <= 2
     (n0, k0) = contrib[0]
-    expr = f"__fmul2_rn(A.vals.v[{n0}], y{k0})"
+    expr = f"A.vals.v[{n0}] * y{k0}"
     if len(contrib) == 2:
         (n1, k1) = contrib[1]
-        expr = f"__ffma2_rn(A.vals.v[{n1}], y{k1}, {expr})"
-    return expr, contrib
+        expr = f"fmaf(A.vals.v[{n1}], y{k1}, {expr})"
+    return f"dup2({expr})", contrib
 
 
 def emit_y_loads(em, ks):
@@ -160,7 +161,7 @@ def emit_y_loads(em, ks):
     for q in sorted({k // 4 for k in ks}):
         em(f"const float4 yq{q} = ysm4[{q}];")
     for k in sorted(ks):
-        em(f"const float2 y{k} = dup2(yq{k // 4}.{'xyzw'[k % 4]});")
+        em(f"const float y{k} = yq{k // 4}.{'xyzw'[k % 4]};")
 
 
 # ---------------------------------------------------------------------------
@@ -316,7 +317,7 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
                         expr, contrib = weight_expr(path, z, j)
                         em(f"  fma_sv(v{j}, {expr}, g);")
                         em(f"  {{ const float2 d = dot_halves(gs, x{j}); " + " ".join(
-                            f"dyp[{k}] = __ffma2_rn(A.vals.v[{n}], d, dyp[{k}]);" for n, k in contrib) + " }")
+                            f"dyp[{k}] = __ffma2_rn(dup2(A.vals.v[{n}]), d, dyp[{k}]);" for n, k in contrib) + " }")
                     em("}")
                 js = path.js
                 em(f"{{ f4 dsv = mul_vv(x{js[0]}, v{js[0]});")
@@ -346,10 +347,10 @@ def emit_variant(em, v):
     em(f"// ===== variant {vid} ({name}): x = {x_irreps}, y = {Y_IRREPS}, filter {OUT_FILTER} =====")
     em(f"namespace {name} {{")
     em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz};")
-    em(f"static constexpr int NW = {nw}, RPC = {v['rpc']}, NST = {v['nst']}, kFwdMinCtas = {v['fmin']}, kFwdRotate = {v['rot']}, kFwdSplit = {v['fsplit']};")
+    em(f"static constexpr int NW = {nw}, RPC = {v['rpc']}, NST = {v['nst']}, kFwdMinCtas = {v['fmin']}, kFwdRotate = {v['rot']}, kFwdSplit = {v['fsplit']}, kFwdCtaWarps = {v['fw'] if v['fsplit'] else v['nw'] * v['rpc']};")
     em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
-    em("struct Vals { float2 v[NNZ]; };  // each value duplicated: operand of packed multiplies")
+    em("struct Vals { float v[NNZ]; };")
     em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N; int64_t E; Vals vals; };")
     em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N; int64_t E; Vals vals; };")
     em()
@@ -369,9 +370,9 @@ def emit_variant(em, v):
     em.end()
     em.end()
     em("template <int C> struct BwdChunkSel;")
-    em("template <> struct BwdChunkSel<-1> { static constexpr int kGBase = 0, kGRows = Z; };  // all chunks")
+    em("template <> struct BwdChunkSel<-1> { static constexpr int kGBase = 0, kGRows = Z, kSlotRows = kBwdSlotRows; };  // all chunks")
     for ci in range(len(chunks)):
-        em(f"template <> struct BwdChunkSel<{ci}> : BwdC{ci} {{}};")
+        em(f"template <> struct BwdChunkSel<{ci}> : BwdC{ci} {{ static constexpr int kSlotRows = BwdC{ci}::kRows; }};")
     em("template <int G> struct FwdGroupSel;")
     for gi in range(len(groups)):
         em(f"template <> struct FwdGroupSel<{gi}> {{ using type = FwdG{gi}; }};")
