@@ -83,6 +83,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_conv_bwd.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp]
     lib.e3j_b200_conv_bwd_phases.restype = c.c_int
     lib.e3j_b200_conv_bwd_phases.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp, i32]
+    lib.e3j_b200_conv_bwd_static.restype = c.c_int
+    lib.e3j_b200_conv_bwd_static.argtypes = [vp] * 12 + [i32, i64, i32, vp]
 
 
 #: every symbol declared in include/e3j_b200.h
@@ -97,6 +99,7 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd_workspace_bytes",
     "e3j_b200_conv_bwd",
     "e3j_b200_conv_bwd_phases",
+    "e3j_b200_conv_bwd_static",
 )
 
 

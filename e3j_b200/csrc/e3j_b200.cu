@@ -315,4 +315,55 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
     return check_launch("convolution_bwd (dx)", debug, stream);
 }
 
+// ---------------------------------------------------------------------------
+// backward without a caller workspace
+// ---------------------------------------------------------------------------
+// Scratch of e3j_b200_conv_bwd_static.  On the host this name is only a handle
+// for the runtime: the device address comes from cudaGetSymbolAddress, once per
+// device, and that address is what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[E3J_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device (looked up on first use).
+int static_scratch(void **out) {
+    int dev = -1;
+    E3JB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices)
+        return set_error(E3J_B200_INTERNAL, "device ordinal out of range for the static scratch table");
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        E3JB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return set_error(E3J_B200_CUDA_RUNTIME, "cudaGetSymbolAddress returned a null address");
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return E3J_B200_OK;
+}
+}  // namespace
+
+int e3j_b200_conv_bwd_static(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                             const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                             const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                             float *ds, int32_t N, int64_t E, int32_t debug, e3j_b200_stream stream) {
+    int rc = check_common(p, N, E);
+    if (rc) return rc;
+    const size_t need = e3j_b200_conv_bwd_workspace_bytes(p, N, E);
+    if (need > (size_t)E3J_B200_STATIC_SCRATCH_BYTES)
+        return set_error(E3J_B200_INVALID_ARGUMENT,
+                         "graph needs " + std::to_string(need) + " bytes of scratch but the built-in array holds " +
+                             std::to_string((size_t)E3J_B200_STATIC_SCRATCH_BYTES) +
+                             "; use e3j_b200_conv_bwd with a caller workspace");
+    void *scratch = nullptr;
+    rc = static_scratch(&scratch);
+    if (rc) return rc;
+    return e3j_b200_conv_bwd_phases(p, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds,
+                                    scratch, (size_t)E3J_B200_STATIC_SCRATCH_BYTES, N, E, debug, stream,
+                                    E3J_B200_BWD_ALL);
+}
+
 }  // extern "C"

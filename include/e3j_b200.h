@@ -140,6 +140,44 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *plan, const float *x, const fl
                              void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
                              int32_t debug, e3j_b200_stream stream, int32_t phases);
 
+/*
+ * Backward for callers that may not allocate device memory.
+ *
+ * Has no counterpart in the reference.  It exists for hosts that run this op
+ * where a device allocation is off limits: under a runtime that owns the whole
+ * device heap and hands a custom call no scratch (an XLA handler bound without
+ * a ScratchAllocator), in a serving process whose memory pool is frozen once
+ * it has started, or in a loop that must never take the allocator's lock.
+ *
+ * Same operands, results and semantics as e3j_b200_conv_bwd, minus the
+ * workspace: the per-edge dx messages (and partial dy buffers) live in a
+ * fixed array inside the library's device image instead,
+ * E3J_B200_STATIC_SCRATCH_BYTES (64 MiB) per GPU that loads the library, held
+ * until the process exits.  A graph whose scratch need
+ * (e3j_b200_conv_bwd_workspace_bytes) exceeds that — about 32 k edges at
+ * X = 4, 8 k at X = 16 with C = 128 — is rejected with
+ * E3J_B200_INVALID_ARGUMENT and a message naming both sizes; nothing is
+ * launched.  The function calls no cudaMalloc / cudaFree and no allocating
+ * library routine.
+ *
+ * The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress, a synchronous runtime query): make that first call
+ * outside any stream capture.  Later calls only enqueue kernels.
+ *
+ * Every call on a device shares the one array and finds the previous call's
+ * bytes in it.  Nothing needs clearing: the per-edge pass rewrites every row
+ * it later reads.  Because the array is shared, two calls whose kernels can
+ * overlap on the GPU (different streams, or different host threads) race on
+ * it: serialise them on one stream.
+ */
+#define E3J_B200_STATIC_SCRATCH_BYTES (64u << 20)
+
+int e3j_b200_conv_bwd_static(const e3j_b200_plan *plan, const float *x, const float *y,
+                             const float *s, const float *dm, const int32_t *sender,
+                             const int32_t *receiver_ptr, const int32_t *sender_ptr_t,
+                             const int32_t *perm_t, float *dx, float *dy, float *ds, int32_t N,
+                             int64_t E, int32_t debug, e3j_b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

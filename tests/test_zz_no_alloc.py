@@ -1,0 +1,79 @@
+"""The workspace-free backward entry point, `e3j_b200_conv_bwd_static`.
+
+Some hosts of this op cannot hand it scratch memory: a runtime that owns the device heap
+and gives custom calls no scratch allocator, a server whose memory pool is frozen after
+start-up, a loop that must not touch the allocator.  For
+them the library carries its own fixed 64 MiB scratch array.  This test drives that
+entry point through the C ABI and demands bit-for-bit the results of the ordinary
+entry point (both are deterministic), on two consecutive calls that share the array —
+the second call finds the first one's bytes in it — and checks that a graph that
+does not fit is refused before anything is launched.
+
+Collected last on purpose: if it fails, every other test has already run.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from e3j_b200 import _lib, ops, problems
+from e3j_b200.convolution import Convolution
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _case(config, nodes, seed):
+    conv = Convolution((problems.X_IRREPS[config], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER")
+    g = problems.make_graph(config, seed, num_nodes=nodes)
+    inp = problems.make_inputs(g, config, conv.num_scalars, conv.source[0].dim, 128, seed)
+    x, y, s = (torch.as_tensor(a).to(DEV) for a in (inp.x, inp.y, inp.s))
+    graph = ops.ConvGraph.build(g.num_nodes, torch.as_tensor(g.sender).to(DEV), torch.as_tensor(g.receiver).to(DEV))
+    dims = (conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128)
+    plan = ops.get_plan(conv._coef_packed, dims, torch.device(DEV))
+    dm = torch.randn((g.num_nodes, conv.target.dim, 128), device=DEV, generator=torch.Generator(DEV).manual_seed(seed))
+    return plan, graph, x, y, s, dm
+
+
+def _bwd_static(plan, graph, x, y, s, dm):
+    ptr_t, perm_t = graph.transposed()
+    dx, dy, ds = torch.full_like(x, float("nan")), torch.full_like(y, float("nan")), torch.full_like(s, float("nan"))
+    rc = _lib.lib().e3j_b200_conv_bwd_static(
+        plan.handle, _ptr(x), _ptr(y), _ptr(s), _ptr(dm), _ptr(graph.sender), _ptr(graph.receiver_ptr), _ptr(ptr_t),
+        _ptr(perm_t), _ptr(dx), _ptr(dy), _ptr(ds), x.shape[0], y.shape[0], 0,
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))  # fmt: skip
+    return rc, (dx, dy, ds)
+
+
+@pytest.mark.parametrize("config,nodes", [(0, 512), (2, 120)])
+def test_static_scratch_matches_workspace_entry_point(config, nodes):
+    for seed in (0, 1):  # two calls in a row: different inputs, one shared scratch array
+        plan, graph, x, y, s, dm = _case(config, nodes, seed)
+        want = ops.conv_bwd_raw(plan, x, y, s, dm, graph)
+        rc, got = _bwd_static(plan, graph, x, y, s, dm)
+        assert rc == 0, _lib.lib().e3j_b200_last_error().decode()
+        torch.cuda.synchronize()
+        for a, b, name in zip(got, want, ("dx", "dy", "ds")):
+            assert torch.equal(a, b), f"{name} differs from e3j_b200_conv_bwd (seed {seed})"
+    # the same call once more, on the inputs of the last round: still identical
+    rc, again = _bwd_static(plan, graph, x, y, s, dm)
+    assert rc == 0
+    for a, b in zip(again, want):
+        assert torch.equal(a, b)
+
+
+def test_oversized_graph_is_refused():
+    plan, graph, x, y, s, dm = _case(1, 4096, 0)  # 134 k edges x 2 KB of dx message > 64 MiB
+    need = _lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, x.shape[0], y.shape[0])
+    assert need > 64 << 20
+    rc, (dx, dy, ds) = _bwd_static(plan, graph, x, y, s, dm)
+    msg = _lib.lib().e3j_b200_last_error().decode()
+    assert rc == 2 and msg.startswith("E3J_ERROR[InvalidArgument]") and str(need) in msg
+    torch.cuda.synchronize()
+    assert torch.isnan(dx).all() and torch.isnan(dy).all()  # nothing ran
