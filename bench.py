@@ -10,10 +10,13 @@ with all operands resident in HBM; `e2e` runs the same step through
 `Convolution.__call__` + autograd with the operands in pinned host memory,
 copied to the device inside the timed region, and reads the loss and dx back.
 
-With N > 1 (torchrun) every rank convolves its own graph of the same
-configuration (different seed) — the reference's data-parallel mode over
-independent graphs, which issues no collective — and the job value is the sum
-of the ranks' edges divided by the slowest rank's time.
+With N > 1 (torchrun) the workload is one graph made of N copies of the config-1
+cube laid along x, split into N slabs, one per GPU; every step exchanges halo
+rows of x (forward) and of dx (backward) between neighbouring ranks over NCCL
+point-to-point, overlapped with the interior receivers.  At N = 1 that graph is
+the config-1 graph itself.  `--workload independent` instead gives every rank
+its own graph (the reference's data-parallel mode, which issues no collective).
+The job value is the total number of edges divided by the slowest rank's time.
 
 `--impl reference` times the CPU oracle port of the reference algorithm
 (OpenMP, all host cores) on a bounded sample of the same workload.
@@ -195,6 +198,8 @@ def run_ours(args):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+        if args.workload != "independent":
+            return run_ours_slab(args, world, rank, local, device)
 
     cfg = args.config
     conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
@@ -347,6 +352,131 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ours_slab(args, world, rank, local, device):
+    """N > 1: one graph of N x 4096 nodes (N cubes of the config-1 workload laid along x,
+    same density and cutoff, open boundaries), split into N slabs; each step exchanges
+    halo rows of x (forward) and of dx (backward) between neighbouring ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from e3j_b200 import ops, problems
+    from e3j_b200.convolution import Convolution
+    from e3j_b200.halo import CudaConvOps, CudaRowOps, HaloConvolution
+    from e3j_b200.harmonics import Harmonics
+    from e3j_b200.partition import elongated_box_graph, partition_slabs
+    from e3j_b200.radial import SILU_2MOM, RadialMLP, bessel_envelope_np
+
+    cfg = 1
+    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
+    g, lo, hi = elongated_box_graph(world, problems.NUM_NODES[cfg], problems.CUTOFF[cfg], seed=0)
+    part = partition_slabs(g.positions, g.sender, g.receiver, world, lo, hi)[rank]
+    plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
+    halo = HaloConvolution(part, (X, Y, Z, S, C), device, CudaConvOps(plan), CudaRowOps)
+
+    gen = torch.Generator(device=device).manual_seed(1 + rank)
+    x_loc = torch.zeros((part.n_loc, X, C), device=device)
+    x_loc[: part.n_own] = torch.randn((part.n_own, X, C), generator=gen, device=device)
+    vec = g.vectors[part.edge_ids]
+    y = torch.as_tensor(Harmonics(3, normalize=True)(vec).astype(np.float32)).to(device)
+    rbf = torch.as_tensor(bessel_envelope_np(np.linalg.norm(vec, axis=1), problems.CUTOFF[cfg], 8).astype(np.float32)).to(device)
+    mlp = RadialMLP.init(8, 64, S * C, 0)
+    w1, w2 = torch.as_tensor(mlp.w1).to(device), torch.as_tensor(mlp.w2).to(device)
+    h = SILU_2MOM * torch.nn.functional.silu(rbf @ w1 / np.sqrt(8))
+    s = (h @ (w2 / np.sqrt(64))).view(-1, S, C).contiguous()
+    e_loc = int(y.shape[0])
+
+    out = torch.empty((part.n_own, Z, C), device=device)
+    dx_loc, dy, ds = torch.empty_like(x_loc), torch.empty_like(y), torch.empty_like(s)
+    halo.forward(x_loc, y, s, out)
+    dm = (2 * out).contiguous()
+
+    def step():
+        halo.forward(x_loc, y, s, out)
+        halo.backward(x_loc, y, s, dm, dx_loc, dy, ds)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_warm, n_warm = time.perf_counter(), 0
+    flag = torch.zeros(1, device=device)
+    while True:  # every rank runs the same number of warm-up steps
+        step()
+        n_warm += 1
+        if n_warm % 16 == 0:
+            flag[0] = float(n_warm >= max(3, args.warmup) and time.perf_counter() - t_warm > 0.6)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if flag.item() > 0:
+                break
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = a.elapsed_time(b)
+
+    # end to end: operands in pinned host memory, copied in every step; loss and dx read back
+    hx, hy, hs = (t.cpu().pin_memory() for t in (x_loc[: part.n_own], y, s))
+    h_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    h_dx = torch.empty((part.n_own, X, C), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x_loc[: part.n_own].copy_(hx, non_blocking=True)
+        y.copy_(hy, non_blocking=True)
+        s.copy_(hs, non_blocking=True)
+        halo.forward(x_loc, y, s, out)
+        loss = (out * out).sum()
+        torch.mul(out, 2.0, out=dm)
+        halo.backward(x_loc, y, s, dm, dx_loc, dy, ds)
+        h_loss.copy_(loss, non_blocking=True)
+        h_dx.copy_(dx_loc[: part.n_own], non_blocking=True)
+
+    e2e_steps = 0 if args.no_e2e else max(2, min(args.steps, 10))
+    for _ in range(0 if args.no_e2e else 2):
+        e2e_step()
+    barrier()
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / max(e2e_steps, 1)
+
+    stats = torch.tensor([ms_total, e2e_ms, float(e_loc), float(part.n_loc - part.n_own)], device=device, dtype=torch.float64)
+    mx, sm = stats.clone(), stats.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms_step = mx[0].item() / args.steps
+        edges_all = sm[2].item()
+        n_peers = len(halo.peers)
+        line = {
+            "metric": METRIC, "value": edges_all / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": n_warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config1 geometry x N: N cubes of 4096 nodes along x (open box, cutoff 4.5 A, "
+                       "x=0e+1o, y=lmax3, out l<=3, C=128), one slab per GPU, fwd+VJP with halo exchange",
+                       "nodes_total": g.num_nodes, "edges_total": int(edges_all), "halo_rows_total": int(sm[3].item()),
+                       "channels": C, "variant": plan.variant, "parallelism": f"slab{world} + p2p halo (NCCL)",
+                       "l2": "inputs larger than L2 (s and ds are %.0f MB each per GPU)" % (s.numel() * 4 / 1e6)},
+            "e2e": None if args.no_e2e else {"value": edges_all / (mx[1].item() * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int((hx.numel() + hy.numel() + hs.numel()) * 4),
+                    "d2h_bytes_per_step": int(h_dx.numel() * 4 + 4), "ms_per_step": mx[1].item()},
+            "gpu_launches": args.steps * (2 + 3 + 2 * n_peers),
+            "clocks": clocks,
+        }  # fmt: skip
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -354,6 +484,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="slab", choices=["slab", "independent"],
+                    help="N > 1: one partitioned graph with halo exchange (default) or one graph per rank")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--nodes", type=int, default=None, help="override the node count (small profiling cases)")

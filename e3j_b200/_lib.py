@@ -83,6 +83,14 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_conv_bwd.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp]
     lib.e3j_b200_conv_bwd_phases.restype = c.c_int
     lib.e3j_b200_conv_bwd_phases.argtypes = [vp] * 13 + [c.c_size_t, i32, i64, i32, vp, i32]
+    lib.e3j_b200_conv_fwd_rect.restype = c.c_int
+    lib.e3j_b200_conv_fwd_rect.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, vp]
+    lib.e3j_b200_conv_bwd_rect.restype = c.c_int
+    lib.e3j_b200_conv_bwd_rect.argtypes = [vp] * 13 + [c.c_size_t, i32, i32, i64, i32, vp, i32]
+    lib.e3j_b200_rows_gather.restype = c.c_int
+    lib.e3j_b200_rows_gather.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.e3j_b200_rows_add.restype = c.c_int
+    lib.e3j_b200_rows_add.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.e3j_b200_conv_bwd_static.restype = c.c_int
     lib.e3j_b200_conv_bwd_static.argtypes = [vp] * 12 + [i32, i64, i32, vp]
 
@@ -100,6 +108,10 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd",
     "e3j_b200_conv_bwd_phases",
     "e3j_b200_conv_bwd_static",
+    "e3j_b200_conv_fwd_rect",
+    "e3j_b200_conv_bwd_rect",
+    "e3j_b200_rows_gather",
+    "e3j_b200_rows_add",
 )
 
 

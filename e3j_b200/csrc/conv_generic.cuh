@@ -46,7 +46,7 @@ __device__ __forceinline__ SmemTable stage_table(const DeviceTable &t, bool in_s
 __global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_kernel(
     DeviceTable table, bool table_in_smem, bool acc_in_smem, const float *__restrict__ x,
     const float *__restrict__ y, const float *__restrict__ s, const int32_t *__restrict__ sender,
-    const int32_t *__restrict__ receiver_ptr, float *__restrict__ out, int32_t N, Dims d) {
+    const int32_t *__restrict__ receiver_ptr, float *__restrict__ out, int32_t N, int32_t NS, Dims d) {
     extern __shared__ __align__(16) float smem_raw[];
     float *smem = smem_raw;
     const SmemTable tab = stage_table(table, table_in_smem, smem);
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_kernel(
             for (int z = 0; z < d.Z; z++) acc[z * astride] = 0.f;
             for (int32_t e = e0; e < e1; e++) {
                 const int32_t a = sender[e];
-                if (!in_range(a, N)) continue;
+                if (!in_range(a, NS)) continue;
                 const float *xa = x + ((int64_t)a * d.X) * C + c;
                 const float *se = s + ((int64_t)e * d.S) * C + c;
                 const float *ye = y + (int64_t)e * d.Y;
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
     DeviceTable table, bool table_in_smem, const float *__restrict__ x, const float *__restrict__ y,
     const float *__restrict__ s, const float *__restrict__ dm, const int32_t *__restrict__ sender,
     const int32_t *__restrict__ receiver_ptr, float *__restrict__ dxm, float *__restrict__ dy,
-    float *__restrict__ ds, int32_t N, Dims d) {
+    float *__restrict__ ds, int32_t N, int32_t NS, Dims d) {
     extern __shared__ __align__(16) float smem_raw[];
     float *smem = smem_raw;
     const SmemTable tab = stage_table(table, table_in_smem, smem);
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
         const float *g = dm + (r * d.Z) * C;
         for (int32_t e = e0; e < e1; e++) {
             const int32_t a = sender[e];
-            const bool valid = in_range(a, N);
+            const bool valid = in_range(a, NS);
             for (int k = 0; k < d.Y; k++) dy_acc[k * CT + tx] = 0.f;
             for (int c0 = 0; c0 < C; c0 += CT) {
                 const int c = c0 + tx;
@@ -236,6 +236,27 @@ __global__ void __launch_bounds__(256) dx_reduce_kernel(const float *__restrict_
             for (int q = 0; q < VEC; q++) of[q] = acc[q];
             reinterpret_cast<V *>(dx + a * XC)[v] = o;
         }
+    }
+}
+
+// Row gather / scatter-add used by the halo exchange of the partitioned mode:
+// dst[i, :] = src[idx[i], :]   and   dst[idx[i], :] += src[i, :]   (idx unique), rows of `row4` float4.
+__global__ void rows_gather_kernel(float4 *__restrict__ dst, const float4 *__restrict__ src,
+                                   const int64_t *__restrict__ idx, int64_t n_rows, int64_t row4) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_rows * row4;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = t / row4, c = t - i * row4;
+        dst[t] = src[idx[i] * row4 + c];
+    }
+}
+__global__ void rows_add_kernel(float4 *__restrict__ dst, const int64_t *__restrict__ idx,
+                                const float4 *__restrict__ src, int64_t n_rows, int64_t row4) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_rows * row4;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = t / row4, c = t - i * row4;
+        float4 *d = dst + idx[i] * row4 + c;
+        const float4 a = *d, b = src[t];
+        *d = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
     }
 }
 

@@ -206,15 +206,22 @@ int check_common(const e3j_b200_plan *p, int32_t N, int64_t E) {
 int e3j_b200_conv_fwd(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
                       const int32_t *sender, const int32_t *receiver_ptr, float *out, int32_t N,
                       int64_t E, int32_t debug, e3j_b200_stream stream) {
+    return e3j_b200_conv_fwd_rect(p, x, y, s, sender, receiver_ptr, out, N, N, E, debug, stream);
+}
+
+int e3j_b200_conv_fwd_rect(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                           const int32_t *sender, const int32_t *receiver_ptr, float *out, int32_t N,
+                           int32_t NS, int64_t E, int32_t debug, e3j_b200_stream stream) {
     int rc = check_common(p, N, E);
     if (rc) return rc;
+    if (NS < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative sender count");
     if (N == 0) return E3J_B200_OK;
     if (!x || !out || !receiver_ptr || (E > 0 && (!y || !s || !sender)))
         return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
 
     if (p->variant != E3J_B200_VARIANT_GENERIC)
         return unrolled::launch_fwd(p->variant, p->un, p->lim.sm_count, x, y, s, sender,
-                                    receiver_ptr, out, N, E, debug, stream);
+                                    receiver_ptr, out, N, NS, E, debug, stream);
 
     const GenericGeometry g = generic_geometry(p);
     const size_t acc_bytes = (size_t)g.block.y * p->d.Z * g.block.x * sizeof(float);
@@ -227,7 +234,7 @@ int e3j_b200_conv_fwd(const e3j_b200_plan *p, const float *x, const float *y, co
     const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
     DeviceTable t{p->d_val, p->d_idx, p->nnz};
     generic::conv_fwd_kernel<<<grid, g.block, smem, stream>>>(t, g.table_in_smem, acc_in_smem, x, y,
-                                                              s, sender, receiver_ptr, out, N, p->d);
+                                                              s, sender, receiver_ptr, out, N, NS, p->d);
     return check_launch("convolution", debug, stream);
 }
 
@@ -255,9 +262,19 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
                              const int32_t *perm_t, float *dx, float *dy, float *ds,
                              void *workspace, size_t workspace_bytes, int32_t N, int64_t E,
                              int32_t debug, e3j_b200_stream stream, int32_t phases) {
+    return e3j_b200_conv_bwd_rect(p, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds,
+                                  workspace, workspace_bytes, N, N, E, debug, stream, phases);
+}
+
+int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                           const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                           const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                           float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                           int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases) {
     int rc = check_common(p, N, E);
     if (rc) return rc;
-    if (N == 0) return E3J_B200_OK;
+    if (NS < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative sender count");
+    if (N == 0 && NS == 0) return E3J_B200_OK;
     if (!x || !dm || !dx || !receiver_ptr || !sender_ptr_t ||
         (E > 0 && (!y || !s || !sender || !perm_t || !dy || !ds)))
         return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
@@ -275,7 +292,7 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
     if (E > 0 && (phases & E3J_B200_BWD_EDGES)) {
         if (p->variant != E3J_B200_VARIANT_GENERIC) {
             rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y, s, dm, sender,
-                                            receiver_ptr, dxm, dy_part, ds, N, E, debug, stream);
+                                            receiver_ptr, dxm, dy_part, ds, N, NS, E, debug, stream);
             if (rc) return rc;
         } else {
             const GenericGeometry g = generic_geometry(p);
@@ -292,7 +309,7 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
             const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
             DeviceTable t{p->d_val, p->d_idx, p->nnz};
             generic::conv_bwd_edges_kernel<<<grid, g.block, smem, stream>>>(
-                t, g.table_in_smem, x, y, s, dm, sender, receiver_ptr, dxm, dy, ds, N, d);
+                t, g.table_in_smem, x, y, s, dm, sender, receiver_ptr, dxm, dy, ds, N, NS, d);
             rc = check_launch("convolution_bwd (edges)", debug, stream);
             if (rc) return rc;
         }
@@ -305,14 +322,51 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
     }
     if (!(phases & E3J_B200_BWD_DX)) return E3J_B200_OK;
     const int64_t XC = (int64_t)d.X * d.C;
-    const int grid = (int)std::min<int64_t>(N, (int64_t)p->lim.sm_count * 16);
+    if (NS == 0) return E3J_B200_OK;
+    const int grid = (int)std::min<int64_t>(NS, (int64_t)p->lim.sm_count * 16);
     const bool vec4 = XC % 4 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
     const int threads = (int)std::min<int64_t>(256, std::max<int64_t>(32, (XC / (vec4 ? 4 : 1) + 31) / 32 * 32));
     if (vec4)
-        generic::dx_reduce_kernel<4><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, N, XC);
+        generic::dx_reduce_kernel<4><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
     else
-        generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, N, XC);
+        generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
     return check_launch("convolution_bwd (dx)", debug, stream);
+}
+
+// ---------------------------------------------------------------------------
+// row gather / scatter-add (halo exchange of the partitioned mode)
+// ---------------------------------------------------------------------------
+static int rows_check(const void *a, const void *b, const void *idx, int64_t n_rows, int64_t row_floats) {
+    if (n_rows < 0 || row_floats <= 0 || row_floats % 4)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "rows must hold a positive multiple of 4 floats");
+    if (n_rows && (!a || !b || !idx)) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b) % 16)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "row buffers must be 16-byte aligned");
+    return E3J_B200_OK;
+}
+
+int e3j_b200_rows_gather(float *dst, const float *src, const int64_t *idx, int64_t n_rows,
+                         int64_t row_floats, e3j_b200_stream stream) {
+    int rc = rows_check(dst, src, idx, n_rows, row_floats);
+    if (rc || n_rows == 0) return rc;
+    const int64_t total = n_rows * (row_floats / 4);
+    const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 16);
+    generic::rows_gather_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<float4 *>(dst),
+                                                           reinterpret_cast<const float4 *>(src), idx, n_rows,
+                                                           row_floats / 4);
+    return check_launch("rows_gather", 0, stream);
+}
+
+int e3j_b200_rows_add(float *dst, const int64_t *idx, const float *src, int64_t n_rows, int64_t row_floats,
+                      e3j_b200_stream stream) {
+    int rc = rows_check(dst, src, idx, n_rows, row_floats);
+    if (rc || n_rows == 0) return rc;
+    const int64_t total = n_rows * (row_floats / 4);
+    const int grid = (int)std::min<int64_t>(ceil_div64(total, 256), 148 * 16);
+    generic::rows_add_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<float4 *>(dst), idx,
+                                                        reinterpret_cast<const float4 *>(src), n_rows,
+                                                        row_floats / 4);
+    return check_launch("rows_add", 0, stream);
 }
 
 // ---------------------------------------------------------------------------

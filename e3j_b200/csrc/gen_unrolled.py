@@ -187,7 +187,7 @@ def emit_fwd_group(em, vname, gi, group, dims):
     em(" ".join(f"c.a{z} = zero_f4();" for z in zs))
     em.end()
     em.block("static __device__ __forceinline__ void prefetch(const FwdArgs &A, int64_t e, int32_t a, float4 *stage, float *ysm, int lane)")
-    em("a = in_range(a, A.N) ? a : 0;")
+    em("a = in_range(a, A.NS) ? a : 0;")
     em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
     em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
     em("float4 *dst = stage + lane;")
@@ -278,7 +278,7 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
         em(f"static constexpr int kRows = {len(srows) + len(xrows)};")
         em(f"static constexpr int kGBase = {g_base}, kGRows = {len(zrows)};  // rows of the staged dm block it reads")
         em.block("static __device__ __forceinline__ void prefetch(const BwdArgs &A, int64_t e, int32_t a, float4 *slot, int lane)")
-        em("a = in_range(a, A.N) ? a : 0;")
+        em("a = in_range(a, A.NS) ? a : 0;")
         em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
         em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
         em("float4 *dst = slot + lane;")
@@ -351,8 +351,8 @@ def emit_variant(em, v):
     em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
     em("struct Vals { float v[NNZ]; };")
-    em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N; int64_t E; Vals vals; };")
-    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N; int64_t E; Vals vals; };")
+    em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N, NS; int64_t E; Vals vals; };")
+    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N, NS; int64_t E; Vals vals; };")
     em()
     if v.get("fwd_groups"):
         groups = [sorted((paths[p] for p in g), key=lambda p: (p.lx, p.p)) for g in v["fwd_groups"]]

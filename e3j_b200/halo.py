@@ -1,0 +1,165 @@
+"""Partitioned convolution: one rank per GPU, halo exchange over `torch.distributed`.
+
+The reference has no such mode (its multi-device path convolves independent graphs
+per device and issues no collective, src/e3j/ops/convolution.py:213-263).  Here a large
+graph is split into spatial slabs (`e3j_b200.partition`); every step
+
+  forward   pack the owned rows the neighbours need -> post sends / receives of halo
+            x rows -> convolve the *interior* receivers (all senders owned) while the
+            halo is in flight -> wait -> convolve the boundary receivers;
+  backward  per-edge pass over the owned receivers -> sum the dx messages per local
+            sender (owned and halo) -> return the halo rows' partial dx to their owners
+            -> owners add them in ascending peer order.
+
+Point-to-point transfers only (each rank talks to the slabs next to it); payloads land
+in this GPU's own memory before any kernel reads them.  The row packing / adding and
+the convolution itself are pluggable so that the exchange logic can be exercised on
+CPU ranks (gloo) with the test oracle standing in for the kernels.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+from .partition import SlabPart
+
+
+class CudaRowOps:
+    """Row gather / scatter-add by the library's kernels on the current stream."""
+
+    @staticmethod
+    def gather(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor) -> None:
+        row = src[0].numel()
+        _lib.check(_lib.lib().e3j_b200_rows_gather(ops._ptr(dst), ops._ptr(src), ops._ptr(idx), idx.numel(), row,
+                                                   ops._stream()))  # fmt: skip
+
+    @staticmethod
+    def add(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> None:
+        row = dst[0].numel()
+        _lib.check(_lib.lib().e3j_b200_rows_add(ops._ptr(dst), ops._ptr(idx), ops._ptr(src), idx.numel(), row,
+                                                ops._stream()))  # fmt: skip
+
+
+class CudaConvOps:
+    """Forward on a receiver sub-range and backward passes through the C ABI."""
+
+    def __init__(self, plan: ops.ConvPlan):
+        self.plan = plan
+        self.workspace = None
+
+    def forward(self, x, y, s, sender, receiver_ptr, out, r0: int, r1: int, n_send: int) -> None:
+        if r1 <= r0:
+            return
+        z, c = self.plan.dims[2], self.plan.dims[4]
+        vp = ctypes.c_void_p
+        _lib.check(_lib.lib().e3j_b200_conv_fwd_rect(
+            self.plan.handle, ops._ptr(x), ops._ptr(y), ops._ptr(s), ops._ptr(sender),
+            vp(receiver_ptr.data_ptr() + 4 * r0), vp(out.data_ptr() + 4 * r0 * z * c), r1 - r0, n_send,
+            int(y.shape[0]), ops.DEBUG_LEVEL, ops._stream()))  # fmt: skip
+
+    def backward(self, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, n_recv, n_send) -> None:
+        e = int(y.shape[0])
+        need = int(_lib.lib().e3j_b200_conv_bwd_workspace_bytes(self.plan.handle, n_recv, e))
+        if self.workspace is None or self.workspace.numel() < need:
+            self.workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        _lib.check(_lib.lib().e3j_b200_conv_bwd_rect(
+            self.plan.handle, ops._ptr(x), ops._ptr(y), ops._ptr(s), ops._ptr(dm), ops._ptr(sender),
+            ops._ptr(receiver_ptr), ops._ptr(sender_ptr_t), ops._ptr(perm_t), ops._ptr(dx), ops._ptr(dy), ops._ptr(ds),
+            ops._ptr(self.workspace), self.workspace.numel(), n_recv, n_send, e, ops.DEBUG_LEVEL, ops._stream(), 7))  # fmt: skip
+
+
+@dataclass
+class _Peer:
+    rank: int
+    send_rows: torch.Tensor | None  # int64 local ids of owned rows this peer needs
+    recv: tuple[int, int] | None  # slice of the halo block this peer fills
+
+
+class HaloConvolution:
+    """The partitioned operator of one rank.
+
+    Args:
+        part: this rank's :class:`SlabPart`.
+        conv_ops / row_ops: compute back ends (CUDA by default).
+        device: where the rank's tensors live.
+        group: process group (default: the world group); ranks are `part.rank`.
+    """
+
+    def __init__(self, part: SlabPart, dims, device, conv_ops, row_ops=CudaRowOps, group=None):
+        self.part, self.device, self.group = part, torch.device(device), group
+        self.conv, self.rows = conv_ops, row_ops
+        self.X, self.Y, self.Z, self.S, self.C = dims
+        to = lambda a, dt: torch.as_tensor(a, dtype=dt).to(self.device)  # noqa: E731
+        self.sender = to(part.sender, torch.int32)
+        self.receiver = to(part.receiver, torch.int32)
+        g = ops.ConvGraph.build(part.n_loc, self.sender, self.receiver)
+        # receiver CSR over the owned receivers only; sender CSR over all local nodes
+        self.receiver_ptr = g.receiver_ptr[: part.n_own + 1].contiguous()
+        self.sender_ptr_t, self.perm_t = g.transposed()
+        self.peers = []
+        for p in part.peers:
+            rows = part.send_rows.get(p)
+            self.peers.append(_Peer(p, None if rows is None else to(rows, torch.int64), part.recv_slice.get(p)))
+        self._send_x = {p.rank: torch.empty((p.send_rows.numel(), self.X, self.C), device=self.device)
+                        for p in self.peers if p.send_rows is not None}  # fmt: skip
+        self._recv_dx = {k: torch.empty_like(v) for k, v in self._send_x.items()}
+
+    # -- exchange -------------------------------------------------------------
+    def _post(self, sends, recvs):
+        opsl = []
+        for peer, buf in recvs:
+            opsl.append(dist.P2POp(dist.irecv, buf, peer, self.group))
+        for peer, buf in sends:
+            opsl.append(dist.P2POp(dist.isend, buf, peer, self.group))
+        return dist.batch_isend_irecv(opsl) if opsl else []
+
+    def start_forward_exchange(self, x_loc: torch.Tensor):
+        """Send owned rows to the peers that need them; receive the halo block in place."""
+        sends, recvs = [], []
+        for p in self.peers:
+            if p.send_rows is not None and p.send_rows.numel():
+                self.rows.gather(self._send_x[p.rank], x_loc, p.send_rows)
+                sends.append((p.rank, self._send_x[p.rank]))
+            if p.recv is not None and p.recv[1] > p.recv[0]:
+                recvs.append((p.rank, x_loc[p.recv[0] : p.recv[1]]))
+        return self._post(sends, recvs)
+
+    def reverse_exchange(self, dx_loc: torch.Tensor) -> None:
+        """Return the halo rows of dx to their owners and add what the peers return."""
+        sends, recvs = [], []
+        for p in self.peers:
+            if p.recv is not None and p.recv[1] > p.recv[0]:
+                sends.append((p.rank, dx_loc[p.recv[0] : p.recv[1]]))
+            if p.send_rows is not None and p.send_rows.numel():
+                recvs.append((p.rank, self._recv_dx[p.rank]))
+        for w in self._post(sends, recvs):
+            w.wait()
+        for p in self.peers:  # ascending peer order: fixed summation order
+            if p.send_rows is not None and p.send_rows.numel():
+                self.rows.add(dx_loc, p.send_rows, self._recv_dx[p.rank])
+
+    # -- operator -------------------------------------------------------------
+    def forward(self, x_loc: torch.Tensor, y: torch.Tensor, s: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """`x_loc` (n_loc, X, C): owned rows filled in, halo block overwritten here.
+        `out` (n_own, Z, C)."""
+        part = self.part
+        works = self.start_forward_exchange(x_loc)
+        self.conv.forward(x_loc, y, s, self.sender, self.receiver_ptr, out, 0, part.n_int, part.n_loc)
+        for w in works:
+            w.wait()
+        self.conv.forward(x_loc, y, s, self.sender, self.receiver_ptr, out, part.n_int, part.n_own, part.n_loc)
+        return out
+
+    def backward(self, x_loc, y, s, dm, dx_loc, dy, ds):
+        """Cotangents for `dm` (n_own, Z, C): `dx_loc` (n_loc rows; on return the owned rows
+        hold the full dx, including what other ranks' edges contributed), `dy`, `ds`."""
+        part = self.part
+        self.conv.backward(x_loc, y, s, dm, self.sender, self.receiver_ptr, self.sender_ptr_t, self.perm_t,
+                           dx_loc, dy, ds, part.n_own, part.n_loc)  # fmt: skip
+        self.reverse_exchange(dx_loc)
+        return dx_loc, dy, ds

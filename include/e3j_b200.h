@@ -141,6 +141,39 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *plan, const float *x, const fl
                              int32_t debug, e3j_b200_stream stream, int32_t phases);
 
 /*
+ * Partitioned mode (no counterpart in the reference, whose multi-device mode is
+ * data parallel over independent graphs, src/e3j/ops/convolution.py:213-263).
+ * A rank of a spatially partitioned graph owns N receivers but gathers from
+ * NS >= N local node rows (its own plus a halo received from neighbours):
+ * x and dx have NS rows, sender indices are valid in [0, NS), sender_ptr_t has
+ * NS + 1 entries; out and dm have N rows, receiver_ptr N + 1 entries.
+ * e3j_b200_conv_fwd / _bwd_phases are the NS == N case.  A sub-range [r0, r1)
+ * of receivers is run by passing receiver_ptr + r0, out + r0 * Z * C and
+ * N = r1 - r0 (edge-indexed operands unchanged), which lets interior receivers
+ * be processed while the halo is still in flight.
+ */
+int e3j_b200_conv_fwd_rect(const e3j_b200_plan *plan, const float *x, const float *y, const float *s,
+                           const int32_t *sender, const int32_t *receiver_ptr, float *out, int32_t N,
+                           int32_t NS, int64_t E, int32_t debug, e3j_b200_stream stream);
+
+int e3j_b200_conv_bwd_rect(const e3j_b200_plan *plan, const float *x, const float *y, const float *s,
+                           const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                           const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                           float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                           int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases);
+
+/*
+ * Halo packing helpers of the partitioned mode: dst[i, :] = src[idx[i], :] and
+ * dst[idx[i], :] += src[i, :] for rows of `row_floats` floats (a multiple of 4,
+ * buffers 16-byte aligned).  `idx` int64[n_rows] must be duplicate-free for
+ * the add, which makes it order independent, hence reproducible.
+ */
+int e3j_b200_rows_gather(float *dst, const float *src, const int64_t *idx, int64_t n_rows,
+                         int64_t row_floats, e3j_b200_stream stream);
+int e3j_b200_rows_add(float *dst, const int64_t *idx, const float *src, int64_t n_rows,
+                      int64_t row_floats, e3j_b200_stream stream);
+
+/*
  * Backward for callers that may not allocate device memory.
  *
  * Has no counterpart in the reference.  It exists for hosts that run this op

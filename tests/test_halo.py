@@ -1,0 +1,209 @@
+"""Partitioned mode: slab partition invariants, the exchange protocol on two CPU ranks
+(gloo) with the oracle standing in for the kernels, and the CUDA path with both ranks
+emulated on one GPU."""
+
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from e3j_b200 import problems
+from e3j_b200.convolution import Convolution
+from e3j_b200.harmonics import Harmonics
+from e3j_b200.partition import elongated_box_graph, partition_slabs
+from oracle import c_oracle
+from tests.conftest import assert_close, csr_ptr
+
+CFG = 0  # x = 0e+1o, cutoff 4.5
+
+
+def _global_case(world, nodes_per_slab=70, channels=128, seed=3):
+    g, lo, hi = elongated_box_graph(world, nodes_per_slab, problems.CUTOFF[CFG], seed=seed)
+    conv = Convolution((problems.X_IRREPS[CFG], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER")
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((g.num_nodes, 4, channels)).astype(np.float32)
+    y = Harmonics(3, normalize=True)(g.vectors).astype(np.float32)
+    s = rng.standard_normal((g.sender.shape[0], conv.num_scalars, channels)).astype(np.float32)
+    dm = rng.standard_normal((g.num_nodes, conv.target.dim, channels)).astype(np.float32)
+    parts = partition_slabs(g.positions, g.sender, g.receiver, world, lo, hi)
+    return g, conv, x, y, s, dm, parts
+
+
+def _global_oracle(g, conv, x, y, s, dm):
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    out = c_oracle.conv_fwd(val, idx4, x, y, s, g.sender, ptr, conv.target.dim)
+    ptr_t, perm_t = c_oracle.transpose_csr(g.sender, g.num_nodes)
+    return (out, *c_oracle.conv_bwd(val, idx4, x, y, s, dm, g.sender, ptr, ptr_t, perm_t))
+
+
+def test_partition_invariants():
+    g, conv, x, y, s, dm, parts = _global_case(3)
+    seen_nodes, seen_edges = [], []
+    for p in parts:
+        assert 0 <= p.n_int <= p.n_own <= p.n_loc and (np.diff(p.receiver) >= 0).all() and (p.receiver < p.n_own).all()
+        # local edges are the global edges of the owned receivers, endpoints mapped consistently
+        assert (p.global_ids[p.sender] == g.sender[p.edge_ids]).all()
+        assert (p.global_ids[p.receiver] == g.receiver[p.edge_ids]).all()
+        # interior receivers only have owned senders
+        assert (p.sender[p.receiver < p.n_int] < p.n_own).all()
+        seen_nodes.append(p.global_ids[: p.n_own])
+        seen_edges.append(p.edge_ids)
+        # the plan is mutually consistent: what p receives from q is what q sends to p, in order
+        for q, (a, b) in p.recv_slice.items():
+            assert (parts[q].global_ids[parts[q].send_rows[p.rank]] == p.global_ids[a:b]).all()
+        assert all(abs(q - p.rank) == 1 for q in p.peers)  # slabs wider than the cutoff: nearest neighbours only
+    assert sorted(np.concatenate(seen_nodes)) == list(range(g.num_nodes))
+    assert sorted(np.concatenate(seen_edges)) == list(range(g.sender.shape[0]))
+
+
+def test_single_slab_is_the_whole_graph():
+    g, conv, x, y, s, dm, parts = _global_case(1)
+    (p,) = parts
+    assert p.n_int == p.n_own == p.n_loc == g.num_nodes and not p.peers
+    # world == 1 reproduces the single-GPU cube workload of the same seed
+    cube = problems.cube_graph(70, problems.CUTOFF[CFG], False, seed=3)
+    assert np.array_equal(cube.sender, g.sender) and np.allclose(cube.positions, g.positions)
+
+
+# ---- oracle-backed compute for CPU ranks ------------------------------------
+class OracleConvOps:
+    def __init__(self, conv):
+        self.val, self.idx4, self.z = conv.coef.val, conv.coef.idx.astype(np.int32), conv.target.dim
+
+    def _ext_ptr(self, receiver_ptr, n_send):
+        ptr = receiver_ptr.numpy()
+        return np.concatenate([ptr, np.full(n_send + 1 - ptr.size, ptr[-1], np.int32)])
+
+    def forward(self, x, y, s, sender, receiver_ptr, out, r0, r1, n_send):
+        if r1 <= r0:
+            return
+        full = c_oracle.conv_fwd(self.val, self.idx4, x.numpy(), y.numpy(), s.numpy(), sender.numpy(),
+                                 self._ext_ptr(receiver_ptr, n_send), self.z)  # fmt: skip
+        out[r0:r1] = torch.from_numpy(full[r0:r1])
+
+    def backward(self, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, n_recv, n_send):
+        dm_ext = np.zeros((n_send,) + tuple(dm.shape[1:]), np.float32)
+        dm_ext[:n_recv] = dm.numpy()
+        gx, gy, gs = c_oracle.conv_bwd(self.val, self.idx4, x.numpy(), y.numpy(), s.numpy(), dm_ext, sender.numpy(),
+                                       self._ext_ptr(receiver_ptr, n_send), sender_ptr_t.numpy(), perm_t.numpy())  # fmt: skip
+        dx.copy_(torch.from_numpy(gx)), dy.copy_(torch.from_numpy(gy)), ds.copy_(torch.from_numpy(gs))
+
+
+class TorchRowOps:
+    @staticmethod
+    def gather(dst, src, idx):
+        dst.copy_(src[idx])
+
+    @staticmethod
+    def add(dst, idx, src):
+        dst[idx] += src
+
+
+def _rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from e3j_b200.halo import HaloConvolution
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g, conv, x, y, s, dm, parts = _global_case(world, channels=8)
+        p = parts[rank]
+        dims = (4, 16, conv.target.dim, conv.num_scalars, 8)
+        halo = HaloConvolution(p, dims, "cpu", OracleConvOps(conv), TorchRowOps)
+        x_loc = torch.full((p.n_loc, 4, 8), float("nan"))
+        x_loc[: p.n_own] = torch.from_numpy(x[p.global_ids[: p.n_own]])
+        y_l, s_l = torch.from_numpy(y[p.edge_ids]), torch.from_numpy(s[p.edge_ids])
+        out = torch.empty((p.n_own, conv.target.dim, 8))
+        halo.forward(x_loc, y_l, s_l, out)
+        dm_l = torch.from_numpy(dm[p.global_ids[: p.n_own]])
+        dx_loc, dy, ds = torch.empty_like(x_loc), torch.empty_like(y_l), torch.empty_like(s_l)
+        halo.backward(x_loc, y_l, s_l, dm_l, dx_loc, dy, ds)
+        ret[rank] = dict(ids=p.global_ids[: p.n_own], eids=p.edge_ids, out=out.numpy(), dx=dx_loc[: p.n_own].numpy(),
+                         dy=dy.numpy(), ds=ds.numpy(), halo_x=x_loc[p.n_own :].numpy(), halo_ids=p.global_ids[p.n_own :])  # fmt: skip
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_exchange_protocol_on_cpu_ranks(world):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(120) for p in procs]
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    g, conv, x, y, s, dm, parts = _global_case(world, channels=8)
+    out, dx, dy, ds = _global_oracle(g, conv, x, y, s, dm)
+    for r in range(world):
+        res = ret[r]
+        assert np.array_equal(res["halo_x"], x[res["halo_ids"]])  # halo rows arrived in place
+        assert_close(res["out"], out[res["ids"]], what=f"out rank {r}")
+        assert_close(res["dx"], dx[res["ids"]], what=f"dx rank {r}")
+        assert_close(res["dy"], dy[res["eids"]], what=f"dy rank {r}")
+        assert_close(res["ds"], ds[res["eids"]], what=f"ds rank {r}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 3])
+def test_cuda_path_with_ranks_emulated_on_one_gpu(world):
+    """The CUDA kernels on sub-ranges and rectangular node counts, row packing and adding;
+    the exchange itself is replaced by direct copies between the emulated ranks."""
+    from e3j_b200 import ops
+    from e3j_b200.halo import CudaConvOps, CudaRowOps, HaloConvolution
+
+    dev = torch.device("cuda:0")
+    g, conv, x, y, s, dm, parts = _global_case(world, nodes_per_slab=300)
+    dims = (4, 16, conv.target.dim, conv.num_scalars, 128)
+    plan = ops.get_plan(conv._coef_packed, dims, dev)
+    assert plan.variant == 1
+    ranks = []
+    for p in parts:
+        h = HaloConvolution(p, dims, dev, CudaConvOps(plan), CudaRowOps)
+        x_loc = torch.full((p.n_loc, 4, 128), float("nan"), device=dev)
+        x_loc[: p.n_own] = torch.from_numpy(x[p.global_ids[: p.n_own]]).to(dev)
+        ranks.append((p, h, x_loc))
+    # emulated forward exchange: pack on the sender with the library's gather, copy into the halo block
+    for p, h, x_loc in ranks:
+        for peer in h.peers:
+            if peer.send_rows is not None:
+                buf = torch.empty((peer.send_rows.numel(), 4, 128), device=dev)
+                CudaRowOps.gather(buf, x_loc, peer.send_rows)
+                a, b = parts[peer.rank].recv_slice[p.rank]
+                ranks[peer.rank][2][a:b] = buf
+    out_g, dx_g, dy_g, ds_g = _global_oracle(g, conv, x, y, s, dm)
+    dx_locs = []
+    for p, h, x_loc in ranks:
+        y_l, s_l = torch.from_numpy(y[p.edge_ids]).to(dev), torch.from_numpy(s[p.edge_ids]).to(dev)
+        out = torch.full((p.n_own, conv.target.dim, 128), float("nan"), device=dev)
+        h.conv.forward(x_loc, y_l, s_l, h.sender, h.receiver_ptr, out, 0, p.n_int, p.n_loc)
+        h.conv.forward(x_loc, y_l, s_l, h.sender, h.receiver_ptr, out, p.n_int, p.n_own, p.n_loc)
+        assert_close(out.cpu().numpy(), out_g[p.global_ids[: p.n_own]], what=f"out rank {p.rank}")
+        dm_l = torch.from_numpy(dm[p.global_ids[: p.n_own]]).to(dev)
+        dx_loc, dy, ds = torch.empty_like(x_loc), torch.empty_like(y_l), torch.empty_like(s_l)
+        h.conv.backward(x_loc, y_l, s_l, dm_l, h.sender, h.receiver_ptr, h.sender_ptr_t, h.perm_t, dx_loc, dy, ds,
+                        p.n_own, p.n_loc)  # fmt: skip
+        assert_close(dy.cpu().numpy(), dy_g[p.edge_ids], what="dy")
+        assert_close(ds.cpu().numpy(), ds_g[p.edge_ids], what="ds")
+        dx_locs.append(dx_loc)
+    # emulated reverse exchange: halo rows go back to their owners and are added there
+    for p, h, _ in ranks:
+        for peer in h.peers:
+            if peer.send_rows is not None:
+                a, b = parts[peer.rank].recv_slice[p.rank]
+                CudaRowOps.add(dx_locs[p.rank], peer.send_rows, dx_locs[peer.rank][a:b].contiguous())
+    for p, h, _ in ranks:
+        assert_close(dx_locs[p.rank][: p.n_own].cpu().numpy(), dx_g[p.global_ids[: p.n_own]], what=f"dx rank {p.rank}")
