@@ -1,0 +1,48 @@
+"""TEST / BENCH INFRASTRUCTURE: builds oracle/_ref/libe3j_ref_conv.so.
+
+Compiles the reference's own CUDA convolution kernels (lib/e3j_ops/cuda/convolution.cu,
+convolution_bwd.cu) for sm_100 straight from the reference tree, plus oracle/ref_shim.cu,
+with nvcc only (the reference's CMake build is not run).  Nothing is copied into this
+repository; the output directory is git-ignored.  Does nothing when the reference tree
+is not mounted.
+
+    python oracle/build_ref.py
+"""
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("E3J_REFERENCE_ROOT", "/root/reference")
+OUT_DIR = os.path.join(HERE, "_ref")
+OUT = os.path.join(OUT_DIR, "libe3j_ref_conv.so")
+
+
+def main() -> int:
+    src = os.path.join(REF, "lib", "e3j_ops")
+    if not os.path.isdir(src):
+        print("reference tree not found: skipping oracle/_ref")
+        return 0
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    os.makedirs(OUT_DIR, exist_ok=True)
+    shim = os.path.join(HERE, "ref_shim.cu")
+    srcs = [os.path.join(src, "cuda", "convolution.cu"), os.path.join(src, "cuda", "convolution_bwd.cu"), shim]
+    if os.path.exists(OUT) and all(os.path.getmtime(OUT) >= os.path.getmtime(s) for s in srcs):
+        print("up to date", OUT)
+        return 0
+    # same code generation target the reference's build lists for Blackwell (CMakeLists.txt:12-18)
+    cmd = [nvcc, "-gencode", "arch=compute_100,code=sm_100", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+           "-Xcompiler", "-fPIC", "-shared", "-I", src, "-o", OUT, *srcs]  # fmt: skip
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode:
+        print(res.stdout[-3000:], res.stderr[-3000:])
+        print("reference kernels did not build: oracle/_ref unavailable")
+        return 1
+    print("built", OUT)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,71 @@
+"""The reference's own CUDA kernels (built into oracle/_ref from the reference tree) beside
+the B200 kernels: same inputs, results compared, timings written for profiles/."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from e3j_b200 import ops, problems
+from e3j_b200.convolution import Convolution
+from oracle import ref_cuda
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref was not built")]
+DEV = "cuda:0"
+
+
+def _setup(config, nodes):
+    dev = torch.device(DEV)
+    conv = Convolution((problems.X_IRREPS[config], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    g = problems.make_graph(config, 0, num_nodes=nodes)
+    x, y, s, _, _ = problems.make_inputs_device(g, config, conv.num_scalars, conv.source[0].dim, dev)
+    dims = (conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128)
+    plan = ops.get_plan(conv._coef_packed, dims, dev)
+    snd, rcv = torch.as_tensor(g.sender).to(dev), torch.as_tensor(g.receiver).to(dev)
+    graph = conv.prepare_graph(g.num_nodes, snd, rcv)
+    ref = ref_cuda.RefConvolution(conv.coef, dims, ops.get_device_properties(), dev)
+    return conv, g, plan, graph, ref, x, y, s, snd, rcv
+
+
+def _time(fn, reps=5):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+@pytest.mark.parametrize("config,nodes", [(1, 4096), (2, 3000)])
+def test_matches_reference_kernels_and_records_timings(config, nodes):
+    conv, g, plan, graph, ref, x, y, s, snd, rcv = _setup(config, nodes)
+    out = ops.conv_fwd_raw(plan, x, y, s, graph)
+    out_ref = ref.forward(x, y, s, graph.sender, graph.receiver_ptr)
+    scale = out_ref.abs().max().item()
+    assert (out - out_ref).abs().max().item() <= 1e-6 + 2e-5 * max(scale, 1.0)
+    dm = 2 * out
+    dx, dy, ds = ops.conv_bwd_raw(plan, x, y, s, dm, graph)
+    perm, recv_t, ptr_t = ref.transpose_graph(graph.sender, graph.receiver, g.num_nodes)
+    rdx, rdy, rds = ref.backward(x, y, s, dm, perm, recv_t, ptr_t)
+    for a, b, name in ((dx, rdx, "dx"), (dy, rdy, "dy"), (ds, rds, "ds")):
+        sc = b.abs().max().item()
+        assert (a - b).abs().max().item() <= 1e-6 + 5e-5 * max(sc, 1.0), name  # the reference's own bwd tolerance
+    res = {
+        "config": config, "nodes": g.num_nodes, "edges": int(g.sender.shape[0]),
+        "ours_fwd_ms": _time(lambda: ops.conv_fwd_raw(plan, x, y, s, graph)),
+        "ours_bwd_ms": _time(lambda: ops.conv_bwd_raw(plan, x, y, s, dm, graph)),
+        "ref_fwd_ms": _time(lambda: ref.forward(x, y, s, graph.sender, graph.receiver_ptr)),
+        "ref_bwd_kernel_ms": _time(lambda: ref.backward(x, y, s, dm, perm, recv_t, ptr_t)),
+        "ref_transpose_ms": _time(lambda: ref.transpose_graph(graph.sender, graph.receiver, g.num_nodes)),
+        "ref_block_y": [ref.by_f, ref.by_b],
+    }  # fmt: skip
+    print("REFCMP", json.dumps(res))
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open(os.path.join("gpurun_out", f"ref_compare_config{config}.json"), "w") as fh:
+        json.dump(res, fh)
