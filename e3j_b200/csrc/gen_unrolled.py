@@ -50,11 +50,11 @@ VARIANTS = [
     # fwd_groups: explicit path groups (else derived); rot = 1 rotates the group -> warp map per CTA
     # fsplit / bsplit = 1 launches one kernel per forward group / backward chunk, so that each
     # kernel's loop stays small enough for the instruction cache
-    # fw = warps per CTA of a split forward kernel
-    dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, fw=4, bw=4, nslot=3, slot_rows=14,
-         bmin=2, bsplit=0, fwd_groups=None),
-    dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=3, slot_rows=14,
-         bmin=2, bsplit=1, fwd_groups=None),
+    # fw = warps per CTA of a split forward kernel; gbuf = 2 double-buffers the staged dm rows
+    dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, fw=4, bw=4, nslot=2, slot_rows=14,
+         bmin=2, bsplit=0, gbuf=2, fwd_groups=None),
+    dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=2, slot_rows=14,
+         bmin=2, bsplit=1, gbuf=2, fwd_groups=None),
 ]
 Y_IRREPS = "0e+1o+2e+3o"
 OUT_FILTER = "0e+1o+2e+3o"
@@ -348,7 +348,7 @@ def emit_variant(em, v):
     em(f"namespace {name} {{")
     em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz};")
     em(f"static constexpr int NW = {nw}, RPC = {v['rpc']}, NST = {v['nst']}, kFwdMinCtas = {v['fmin']}, kFwdRotate = {v['rot']}, kFwdSplit = {v['fsplit']}, kFwdCtaWarps = {v['fw'] if v['fsplit'] else v['nw'] * v['rpc']};")
-    em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']};")
+    em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']}, kBwdGBuf = {v.get('gbuf', 1)};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
     em("struct Vals { float v[NNZ]; };")
     em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N, NS; int64_t E; Vals vals; };")
