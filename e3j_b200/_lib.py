@@ -91,6 +91,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_rows_gather.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.e3j_b200_rows_add.restype = c.c_int
     lib.e3j_b200_rows_add.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.e3j_b200_harmonics_fwd.restype = c.c_int
+    lib.e3j_b200_harmonics_fwd.argtypes = [vp, vp, i32, i32, i32, vp, vp, i64, vp]
+    lib.e3j_b200_harmonics_bwd.restype = c.c_int
+    lib.e3j_b200_harmonics_bwd.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, i64, vp]
     lib.e3j_b200_conv_bwd_static.restype = c.c_int
     lib.e3j_b200_conv_bwd_static.argtypes = [vp] * 12 + [i32, i64, i32, vp]
 
@@ -112,6 +116,8 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd_rect",
     "e3j_b200_rows_gather",
     "e3j_b200_rows_add",
+    "e3j_b200_harmonics_fwd",
+    "e3j_b200_harmonics_bwd",
 )
 
 

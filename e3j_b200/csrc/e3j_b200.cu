@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "conv_generic.cuh"
 #include "conv_unrolled.cuh"
+#include "harmonics.cuh"
 
 namespace e3jb {
 
@@ -331,6 +332,40 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *
     else
         generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
     return check_launch("convolution_bwd (dx)", debug, stream);
+}
+
+// ---------------------------------------------------------------------------
+// harmonics of edge vectors
+// ---------------------------------------------------------------------------
+static int harmonics_check(const float *coef, const int32_t *desc, int32_t M, int32_t dim, int64_t E) {
+    if (M <= 0 || dim <= 0 || dim > harmonics::kMaxDim || E < 0)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "harmonics table: need 0 < M, 0 < dim <= 64, E >= 0");
+    if (!coef || !desc) return set_error(E3J_B200_INVALID_ARGUMENT, "harmonics table is null");
+    if ((size_t)M * 8 > 48 * 1024) return set_error(E3J_B200_UNIMPLEMENTED, "harmonics table too large");
+    return E3J_B200_OK;
+}
+
+int e3j_b200_harmonics_fwd(const float *mono_coef, const int32_t *mono_desc, int32_t M, int32_t dim,
+                           int32_t normalize, const float *r, float *y, int64_t E, e3j_b200_stream stream) {
+    int rc = harmonics_check(mono_coef, mono_desc, M, dim, E);
+    if (rc || E == 0) return rc;
+    if (!r || !y) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    harmonics::Table t{mono_coef, mono_desc, M, dim, normalize};
+    const int grid = (int)std::min<int64_t>(ceil_div64(E, 128), 148 * 16);
+    harmonics::fwd_kernel<<<grid, 128, (size_t)M * 8, stream>>>(t, r, y, E);
+    return check_launch("harmonics", 0, stream);
+}
+
+int e3j_b200_harmonics_bwd(const float *mono_coef, const int32_t *mono_desc, int32_t M, int32_t dim,
+                           int32_t normalize, const float *r, const float *dy, float *dr, int64_t E,
+                           e3j_b200_stream stream) {
+    int rc = harmonics_check(mono_coef, mono_desc, M, dim, E);
+    if (rc || E == 0) return rc;
+    if (!r || !dy || !dr) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    harmonics::Table t{mono_coef, mono_desc, M, dim, normalize};
+    const int grid = (int)std::min<int64_t>(ceil_div64(E, 128), 148 * 16);
+    harmonics::bwd_kernel<<<grid, 128, (size_t)M * 8, stream>>>(t, r, dy, dr, E);
+    return check_launch("harmonics_bwd", 0, stream);
 }
 
 // ---------------------------------------------------------------------------

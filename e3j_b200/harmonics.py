@@ -193,6 +193,21 @@ class Harmonics:
         r = np.asarray(r)
         return self.polynomial(self.project(r))
 
+    def cuda(self, r):
+        """Evaluate on a CUDA tensor (E, 3) -> (E, dim) with the library kernel; differentiable
+        with respect to `r` (first order)."""
+        import torch
+
+        key = str(r.device)
+        cache = self.__dict__.setdefault("_device_tables", {})
+        if key not in cache:
+            e = self.mono_exp.astype(np.int64)
+            desc = (e[:, 0] | (e[:, 1] << 4) | (e[:, 2] << 8) | (self.mono_row.astype(np.int64) << 12)).astype(np.int32)
+            cache[key] = (torch.as_tensor(self.mono_coef.astype(np.float32)).to(r.device),
+                          torch.as_tensor(desc).to(r.device))  # fmt: skip
+        coef, desc = cache[key]
+        return _HarmonicsFn.get().apply(r, coef, desc, self.dim, self.normalize)
+
     def vjp(self, r: np.ndarray, dy: np.ndarray) -> np.ndarray:
         """Cotangent of ``r`` given the cotangent ``dy`` of the output."""
         r = np.asarray(r)
@@ -215,6 +230,55 @@ class Harmonics:
         n = np.sqrt(np.sum(r * r, axis=-1) + r.dtype.type(SAFE_NORM_EPS))[:, None]
         # u = r / n  =>  dr = du / n - r (r . du) / n**3
         return du / n - r * np.sum(r * du, axis=-1, keepdims=True) / n**3
+
+
+class _HarmonicsFn:
+    """Lazy holder of the torch autograd function (torch is imported on first use)."""
+
+    fn = None
+
+    @classmethod
+    def get(cls):
+        if cls.fn is None:
+            import ctypes
+
+            import torch
+
+            from . import _lib
+
+            def ptr(t):
+                return ctypes.c_void_p(t.data_ptr())
+
+            def stream():
+                return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+            class HarmonicsFunction(torch.autograd.Function):
+                @staticmethod
+                def forward(ctx, r, coef, desc, dim, normalize):
+                    if r.device.type != "cuda":
+                        raise RuntimeError("Harmonics.cuda runs on CUDA tensors only; use __call__ for numpy arrays")
+                    r = r.contiguous().float()
+                    y = torch.empty((r.shape[0], dim), device=r.device, dtype=torch.float32)
+                    with torch.cuda.device(r.device):
+                        _lib.check(_lib.lib().e3j_b200_harmonics_fwd(ptr(coef), ptr(desc), coef.numel(), dim,
+                                                                      int(normalize), ptr(r), ptr(y), r.shape[0], stream()))  # fmt: skip
+                    ctx.save_for_backward(r, coef, desc)
+                    ctx.meta = (dim, normalize)
+                    return y
+
+                @staticmethod
+                def backward(ctx, dy):
+                    r, coef, desc = ctx.saved_tensors
+                    dim, normalize = ctx.meta
+                    dy = dy.contiguous().float()
+                    dr = torch.empty_like(r)
+                    with torch.cuda.device(r.device):
+                        _lib.check(_lib.lib().e3j_b200_harmonics_bwd(ptr(coef), ptr(desc), coef.numel(), dim,
+                                                                      int(normalize), ptr(r), ptr(dy), ptr(dr), r.shape[0], stream()))  # fmt: skip
+                    return dr, None, None, None, None
+
+            cls.fn = HarmonicsFunction
+        return cls.fn
 
 
 def wigner_D(l: int, rot: np.ndarray, *, seed: int = 0) -> np.ndarray:  # noqa: E741, N802

@@ -174,6 +174,23 @@ int e3j_b200_rows_add(float *dst, const int64_t *idx, const float *src, int64_t 
                       int64_t row_floats, e3j_b200_stream stream);
 
 /*
+ * Real harmonics of edge vectors, the producer of `y`, and their vector-Jacobian
+ * product (the gradient with respect to positions flows through it).  Replaces the XLA
+ * evaluation of e3j.core.Harmonics.__call__ (src/e3j/core/harmonics.py:93-101: optional
+ * projection with the safe norm of src/e3j/utils/safe.py:24-46, then the polynomial of
+ * src/e3j/core/polynomials.py).  The polynomial arrives as a monomial table in device
+ * memory, built on the host from the reference's ladder construction: `mono_coef`
+ * float[M] and `mono_desc` int32[M] = i | j << 4 | k << 8 | row << 12 for the term
+ * coef * a^i b^j c^k of output component `row`, rows in ascending order.
+ *   r float[E, 3] -> y float[E, dim];   dy float[E, dim] -> dr float[E, 3].
+ */
+int e3j_b200_harmonics_fwd(const float *mono_coef, const int32_t *mono_desc, int32_t M, int32_t dim,
+                           int32_t normalize, const float *r, float *y, int64_t E, e3j_b200_stream stream);
+int e3j_b200_harmonics_bwd(const float *mono_coef, const int32_t *mono_desc, int32_t M, int32_t dim,
+                           int32_t normalize, const float *r, const float *dy, float *dr, int64_t E,
+                           e3j_b200_stream stream);
+
+/*
  * Backward for callers that may not allocate device memory.
  *
  * Has no counterpart in the reference.  It exists for hosts that run this op
