@@ -91,6 +91,12 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_rows_gather.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.e3j_b200_rows_add.restype = c.c_int
     lib.e3j_b200_rows_add.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.e3j_b200_csr_ptr.restype = c.c_int
+    lib.e3j_b200_csr_ptr.argtypes = [vp, i64, i32, vp, vp]
+    lib.e3j_b200_csr_transpose_workspace_bytes.restype = c.c_size_t
+    lib.e3j_b200_csr_transpose_workspace_bytes.argtypes = [i32, i64]
+    lib.e3j_b200_csr_transpose.restype = c.c_int
+    lib.e3j_b200_csr_transpose.argtypes = [vp, i64, i32, vp, vp, vp, c.c_size_t, vp]
     lib.e3j_b200_harmonics_fwd.restype = c.c_int
     lib.e3j_b200_harmonics_fwd.argtypes = [vp, vp, i32, i32, i32, vp, vp, i64, vp]
     lib.e3j_b200_harmonics_bwd.restype = c.c_int
@@ -116,6 +122,9 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd_rect",
     "e3j_b200_rows_gather",
     "e3j_b200_rows_add",
+    "e3j_b200_csr_ptr",
+    "e3j_b200_csr_transpose_workspace_bytes",
+    "e3j_b200_csr_transpose",
     "e3j_b200_harmonics_fwd",
     "e3j_b200_harmonics_bwd",
 )

@@ -1,0 +1,82 @@
+// CSR construction on the device: segment offsets of an index array and the stable
+// transposition (edges re-sorted by sender) the backward pass needs.
+//
+// Replaces the XLA bincount + cumsum and the full argsort the reference runs on every
+// call (src/e3j/data/graph.py:53-56, 59-72).  Indices outside [0, N) are padding: they
+// are counted in an extra bucket N, so they land behind every real segment, in order.
+// The transposition is a counting sort: histogram, scan, unordered bucket fill, then a
+// per-segment sort of the edge ids, which makes the result independent of the order in
+// which the fill's atomics were served (it equals a stable argsort by sender).
+#pragma once
+
+#include "common.cuh"
+
+namespace e3jb {
+namespace csr {
+
+__device__ __forceinline__ int32_t bucket_of(int32_t a, int32_t N) { return in_range(a, N) ? a : N; }
+
+// counts[b + 1] += 1 for every index (counts has N + 2 entries, zeroed beforehand)
+__global__ void histogram_kernel(const int32_t *__restrict__ index, int64_t E, int32_t N, int32_t *__restrict__ counts) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x)
+        atomicAdd(&counts[bucket_of(index[e], N) + 1], 1);
+}
+
+// in-place inclusive scan of `n` ints by one CTA of 1024 threads (each owns a contiguous slice)
+__global__ void __launch_bounds__(1024) scan_kernel(int32_t *__restrict__ data, int64_t n) {
+    __shared__ int32_t part[1024];
+    const int64_t per = (n + 1023) / 1024, lo = min(n, per * threadIdx.x), hi = min(n, lo + per);
+    int32_t sum = 0;
+    for (int64_t i = lo; i < hi; i++) sum += data[i];
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {  // Hillis-Steele over the 1024 slice totals
+        const int32_t v = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+        __syncthreads();
+        part[threadIdx.x] += v;
+        __syncthreads();
+    }
+    int32_t run = threadIdx.x ? part[threadIdx.x - 1] : 0;
+    for (int64_t i = lo; i < hi; i++) {
+        run += data[i];
+        data[i] = run;
+    }
+}
+
+// perm[ptr[b] + (arrival order)] = e; cursor has N + 1 entries, zeroed beforehand
+__global__ void fill_kernel(const int32_t *__restrict__ index, int64_t E, int32_t N, const int32_t *__restrict__ ptr,
+                            int32_t *__restrict__ cursor, int32_t *__restrict__ perm) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t b = bucket_of(index[e], N);
+        perm[ptr[b] + atomicAdd(&cursor[b], 1)] = (int32_t)e;
+    }
+}
+
+// Sorts every segment of `perm` ascending.  One warp per segment; the ids are unique, so
+// the rank of an id (how many ids of the segment are smaller) is its final position.  The
+// segment streams through shared memory in tiles of 1024 ids; ranks are written to `out`.
+__global__ void __launch_bounds__(128) sort_segments_kernel(const int32_t *__restrict__ ptr, int32_t num_segments,
+                                                            const int32_t *__restrict__ perm, int32_t *__restrict__ out) {
+    __shared__ int32_t tile_all[4][1024];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t *tile = tile_all[warp];
+    for (int64_t sgm = (int64_t)blockIdx.x * 4 + warp; sgm < num_segments; sgm += (int64_t)gridDim.x * 4) {
+        const int32_t b = ptr[sgm], n = ptr[sgm + 1] - b;
+        if (n <= 0) continue;
+        for (int32_t i0 = 0; i0 < n; i0 += 32) {  // 32 ids ranked at a time
+            const int32_t mine = (i0 + lane < n) ? perm[b + i0 + lane] : 0x7fffffff;
+            int32_t rank = 0;
+            for (int32_t t0 = 0; t0 < n; t0 += 1024) {
+                const int32_t tn = min(1024, n - t0);
+                __syncwarp();
+                for (int32_t t = lane; t < tn; t += 32) tile[t] = perm[b + t0 + t];
+                __syncwarp();
+                for (int32_t t = 0; t < tn; t++) rank += tile[t] < mine;
+            }
+            if (i0 + lane < n) out[b + rank] = mine;
+        }
+    }
+}
+
+}  // namespace csr
+}  // namespace e3jb

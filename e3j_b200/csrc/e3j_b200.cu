@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "conv_generic.cuh"
 #include "conv_unrolled.cuh"
+#include "csr.cuh"
 #include "harmonics.cuh"
 
 namespace e3jb {
@@ -332,6 +333,45 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *
     else
         generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
     return check_launch("convolution_bwd (dx)", debug, stream);
+}
+
+// ---------------------------------------------------------------------------
+// CSR construction
+// ---------------------------------------------------------------------------
+int e3j_b200_csr_ptr(const int32_t *index, int64_t E, int32_t N, int32_t *ptr, e3j_b200_stream stream) {
+    if (N < 0 || E < 0 || !ptr || (E > 0 && !index)) return set_error(E3J_B200_INVALID_ARGUMENT, "bad CSR operands");
+    if (E > 0x7fffffffLL) return set_error(E3J_B200_INVALID_ARGUMENT, "edge count exceeds int32 offsets");
+    E3JB_CUDA_TRY(cudaMemsetAsync(ptr, 0, sizeof(int32_t) * ((size_t)N + 2), stream));
+    if (E > 0) {
+        const int grid = (int)std::min<int64_t>(ceil_div64(E, 256), 148 * 8);
+        csr::histogram_kernel<<<grid, 256, 0, stream>>>(index, E, N, ptr);
+    }
+    csr::scan_kernel<<<1, 1024, 0, stream>>>(ptr, (int64_t)N + 2);
+    return check_launch("csr_ptr", 0, stream);
+}
+
+size_t e3j_b200_csr_transpose_workspace_bytes(int32_t N, int64_t E) {
+    return (((size_t)std::max(N, 0) + 1) * sizeof(int32_t) + 255) / 256 * 256 +
+           ((size_t)std::max<int64_t>(E, 0) * sizeof(int32_t) + 255) / 256 * 256;
+}
+
+int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t *sender_ptr_t, int32_t *perm_t,
+                           void *workspace, size_t workspace_bytes, e3j_b200_stream stream) {
+    if (N < 0 || E < 0 || !sender_ptr_t || (E > 0 && (!sender || !perm_t)))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "bad CSR operands");
+    if (workspace_bytes < e3j_b200_csr_transpose_workspace_bytes(N, E) || !workspace)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "workspace is too small");
+    int rc = e3j_b200_csr_ptr(sender, E, N, sender_ptr_t, stream);
+    if (rc || E == 0) return rc;
+    int32_t *cursor = static_cast<int32_t *>(workspace);
+    int32_t *unsorted = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) +
+                                                    (((size_t)N + 1) * sizeof(int32_t) + 255) / 256 * 256);
+    E3JB_CUDA_TRY(cudaMemsetAsync(cursor, 0, sizeof(int32_t) * ((size_t)N + 1), stream));
+    const int grid = (int)std::min<int64_t>(ceil_div64(E, 256), 148 * 8);
+    csr::fill_kernel<<<grid, 256, 0, stream>>>(sender, E, N, sender_ptr_t, cursor, unsorted);
+    const int sgrid = (int)std::min<int64_t>(ceil_div64((int64_t)N + 1, 4), 148 * 16);
+    csr::sort_segments_kernel<<<sgrid, 128, 0, stream>>>(sender_ptr_t, N + 1, unsorted, perm_t);
+    return check_launch("csr_transpose", 0, stream);
 }
 
 // ---------------------------------------------------------------------------

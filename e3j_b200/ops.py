@@ -112,13 +112,31 @@ class ConvGraph:
     def build(cls, num_nodes: int, sender: torch.Tensor, receiver: torch.Tensor) -> "ConvGraph":
         sender = sender.to(torch.int32).contiguous()
         receiver = receiver.to(torch.int32).contiguous()
+        if receiver.device.type == "cuda":
+            ptr = torch.empty(num_nodes + 2, dtype=torch.int32, device=receiver.device)
+            with torch.cuda.device(receiver.device):
+                _lib.check(_lib.lib().e3j_b200_csr_ptr(_ptr(receiver), receiver.numel(), num_nodes, _ptr(ptr), _stream()))
+            return cls(int(num_nodes), sender, receiver, ptr[: num_nodes + 1])
         return cls(int(num_nodes), sender, receiver, receiver_ptr_from_sorted(num_nodes, receiver))
 
     def transposed(self):
+        """Sender CSR offsets and the stable edge permutation of ``GraphCSR.transpose``
+        (src/e3j/data/graph.py:59-72), computed once per graph."""
         if self.perm_t is None:
-            perm, graph_t, _ = GraphCSR(self.num_nodes, self.sender, self.receiver).transpose()
-            self.perm_t = perm.contiguous()
-            self.sender_ptr_t = graph_t.receiver_ptr.contiguous()
+            if self.sender.device.type == "cuda":
+                dev, e, n = self.sender.device, self.sender.numel(), self.num_nodes
+                ptr_t = torch.empty(n + 2, dtype=torch.int32, device=dev)
+                perm = torch.empty(max(e, 1), dtype=torch.int32, device=dev)
+                need = int(_lib.lib().e3j_b200_csr_transpose_workspace_bytes(n, e))
+                ws = torch.empty(need, dtype=torch.uint8, device=dev)
+                with torch.cuda.device(dev):
+                    _lib.check(_lib.lib().e3j_b200_csr_transpose(_ptr(self.sender), e, n, _ptr(ptr_t), _ptr(perm),
+                                                                 _ptr(ws), need, _stream()))  # fmt: skip
+                self.perm_t, self.sender_ptr_t = perm[:e], ptr_t[: n + 1]
+            else:
+                perm, graph_t, _ = GraphCSR(self.num_nodes, self.sender, self.receiver).transpose()
+                self.perm_t = perm.contiguous()
+                self.sender_ptr_t = graph_t.receiver_ptr.contiguous()
         return self.sender_ptr_t, self.perm_t
 
 

@@ -174,6 +174,22 @@ int e3j_b200_rows_add(float *dst, const int64_t *idx, const float *src, int64_t 
                       int64_t row_floats, e3j_b200_stream stream);
 
 /*
+ * CSR construction on the device, replacing the XLA ops of GraphCSR
+ * (src/e3j/data/graph.py:38-72).  `ptr` / `sender_ptr_t` have N + 2 entries: entry N + 1
+ * closes an extra bucket that collects the padding indices (outside [0, N)), so
+ * ptr[0 .. N] are the CSR offsets the kernels take.
+ *   csr_ptr        ptr[n] = #{e : index[e] < n}, i.e. cumsum(bincount(index)) (:53-56).
+ *   csr_transpose  sender_ptr_t as above for `sender`, and perm_t[p] = index of the p-th edge
+ *                  in sender order, ties in ascending edge index: the stable argsort of
+ *                  GraphCSR.transpose() (:59-72), padding edges last.  Deterministic.
+ * `workspace`: e3j_b200_csr_transpose_workspace_bytes(N, E) bytes of device scratch.
+ */
+int e3j_b200_csr_ptr(const int32_t *index, int64_t E, int32_t N, int32_t *ptr, e3j_b200_stream stream);
+size_t e3j_b200_csr_transpose_workspace_bytes(int32_t N, int64_t E);
+int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t *sender_ptr_t, int32_t *perm_t,
+                           void *workspace, size_t workspace_bytes, e3j_b200_stream stream);
+
+/*
  * Real harmonics of edge vectors, the producer of `y`, and their vector-Jacobian
  * product (the gradient with respect to positions flows through it).  Replaces the XLA
  * evaluation of e3j.core.Harmonics.__call__ (src/e3j/core/harmonics.py:93-101: optional

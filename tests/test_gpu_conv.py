@@ -302,3 +302,27 @@ def test_errors_are_reported_not_thrown_across_the_abi():
     assert rc == 2 and "dtype pair" in lib.e3j_b200_last_error().decode()
     props = ops.get_device_properties()
     assert props["smem_opt_in"] >= 200 * 1024 and props["regs_per_sm"] == 65536
+
+
+@pytest.mark.parametrize("n,e,pad", [(1, 0, 0), (7, 40, 0), (300, 9000, 17), (5000, 200000, 128), (3, 5000, 3)])
+def test_device_csr_matches_stable_argsort(n, e, pad):
+    """e3j_b200_csr_ptr / _csr_transpose against bincount + cumsum and a stable argsort
+    (src/e3j/data/graph.py:53-72), padding indices included."""
+    from e3j_b200.graph import DUMMY_INDEX, GraphCSR
+
+    rng = np.random.default_rng(n + e)
+    snd = rng.integers(0, n, e).astype(np.int32)
+    rcv = np.sort(rng.integers(0, n, e)).astype(np.int32)
+    if pad:
+        where = rng.choice(e, pad, replace=False)
+        snd[where] = DUMMY_INDEX
+        rcv = np.concatenate([rcv[: e - pad], np.full(pad, DUMMY_INDEX, np.int32)])
+    g = ops.ConvGraph.build(n, dev(snd), dev(rcv))
+    ptr_t, perm_t = g.transposed()
+    ref = GraphCSR(n, torch.as_tensor(snd), torch.as_tensor(rcv))
+    assert g.receiver_ptr.cpu().tolist() == ref.receiver_ptr.tolist()
+    perm_ref, gt, _ = ref.transpose()
+    assert ptr_t.cpu().tolist() == gt.receiver_ptr.tolist()
+    assert perm_t.cpu().tolist() == perm_ref.tolist()  # padding edges last, in order
+    again = ops.ConvGraph.build(n, dev(snd), dev(rcv)).transposed()[1]
+    assert torch.equal(again, perm_t)
