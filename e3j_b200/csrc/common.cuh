@@ -88,6 +88,12 @@ __device__ __forceinline__ void fma_vv(f4 &d, const f4 &a, const f4 &b) {
 __device__ __forceinline__ float2 dot_halves(const f4 &a, const f4 &b) {
     return __ffma2_rn(a.hi, b.hi, __fmul2_rn(a.lo, b.lo));
 }
+// dy accumulation: acc += val * (d.x + d.y), either kept per half (one packed multiply-add)
+// or folded to a scalar first (one add + one scalar multiply-add, 16 fewer registers).
+__device__ __forceinline__ void dy_add(float2 &acc, float val, const float2 &d) { acc = __ffma2_rn(dup2(val), d, acc); }
+__device__ __forceinline__ void dy_add(float &acc, float val, const float2 &d) { acc = fmaf(val, d.x + d.y, acc); }
+__device__ __forceinline__ float dy_total(const float2 &v) { return v.x + v.y; }
+__device__ __forceinline__ float dy_total(float v) { return v; }
 __device__ __forceinline__ void st_stream4(float4 *p, const f4 &v) { __stcs(p, as_float4(v)); }
 
 // ---- 16-byte asynchronous global -> shared copies (one per lane) ------------

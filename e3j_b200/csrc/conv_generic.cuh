@@ -182,10 +182,24 @@ __global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int3
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     if (nparts > 1) {
-        for (int64_t t = tid; t < first * dy_row; t += step) {
-            float v = dy_part[t];
-            for (int p = 1; p < nparts; p++) v += dy_part[(int64_t)p * E * dy_row + t];
-            dy[t] = v;
+        const int64_t total = first * dy_row, part = E * dy_row;
+        if ((dy_row & 3) == 0) {  // rows of whole float4: 128-bit accesses
+            const float4 *p4 = reinterpret_cast<const float4 *>(dy_part);
+            float4 *o4 = reinterpret_cast<float4 *>(dy);
+            for (int64_t t = tid; t < total / 4; t += step) {
+                float4 v = p4[t];
+                for (int p = 1; p < nparts; p++) {
+                    const float4 u = p4[(int64_t)p * (part / 4) + t];
+                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+                }
+                o4[t] = v;
+            }
+        } else {
+            for (int64_t t = tid; t < total; t += step) {
+                float v = dy_part[t];
+                for (int p = 1; p < nparts; p++) v += dy_part[(int64_t)p * part + t];
+                dy[t] = v;
+            }
         }
     }
     for (int64_t t = first * dxm_row + tid; t < E * dxm_row; t += step) dxm[t] = 0.f;

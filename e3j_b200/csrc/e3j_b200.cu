@@ -317,7 +317,7 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *
         }
     }
     if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
-        generic::bwd_finish_kernel<<<p->lim.sm_count * 4, 256, 0, stream>>>(
+        generic::bwd_finish_kernel<<<p->lim.sm_count * 8, 256, 0, stream>>>(
             receiver_ptr, N, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
         rc = check_launch("convolution_bwd (tail)", debug, stream);
         if (rc) return rc;

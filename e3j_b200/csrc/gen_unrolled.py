@@ -287,7 +287,7 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
         for j in xrows:
             em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
         em.end()
-        em.block("static __device__ __forceinline__ void compute(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float2 (&dyp)[16])")
+        em.block("static __device__ __forceinline__ void compute(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, DyAcc (&dyp)[16])")
         em(f"float4 *ds_out = reinterpret_cast<float4 *>(A.ds + (e * {S}) * 128) + lane;")
         em(f"float4 *dx_out = reinterpret_cast<float4 *>(A.dxm + (e * {X}) * 128) + lane;")
         em("const f4 zero4 = zero_f4();")
@@ -317,7 +317,7 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
                         expr, contrib = weight_expr(path, z, j)
                         em(f"  fma_sv(v{j}, {expr}, g);")
                         em(f"  {{ const float2 d = dot_halves(gs, x{j}); " + " ".join(
-                            f"dyp[{k}] = __ffma2_rn(dup2(A.vals.v[{n}]), d, dyp[{k}]);" for n, k in contrib) + " }")
+                            f"dy_add(dyp[{k}], A.vals.v[{n}], d);" for n, k in contrib) + " }")
                     em("}")
                 js = path.js
                 em(f"{{ f4 dsv = mul_vv(x{js[0]}, v{js[0]});")
@@ -351,6 +351,7 @@ def emit_variant(em, v):
     em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']}, kBwdGBuf = {v.get('gbuf', 1)};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
     em("struct Vals { float v[NNZ]; };")
+    em(f"using DyAcc = {'float' if v.get('dyscalar') else 'float2'};  // per-lane accumulator of one dy component")
     em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N, NS; int64_t E; Vals vals; };")
     em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N, NS; int64_t E; Vals vals; };")
     em()
@@ -382,7 +383,7 @@ def emit_variant(em, v):
         em(f"case {ci}: BwdC{ci}::prefetch(A, e, a, slot, lane); break;")
     em.end()
     em.end()
-    em.block("__device__ __forceinline__ void bwd_compute_step(int c, const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, float2 (&dyp)[16])")
+    em.block("__device__ __forceinline__ void bwd_compute_step(int c, const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, DyAcc (&dyp)[16])")
     em.block("switch (c)")
     for ci in range(len(chunks)):
         em(f"case {ci}: BwdC{ci}::compute(A, sg, gsm, ysm, e, valid, lane, dyp); break;")
