@@ -60,6 +60,49 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+XLA_LIB_PATH = os.path.join(_HERE, "libe3j_b200_xla.so")
+
+
+def xla_ffi_include_dir() -> str | None:
+    """Root under which `xla/ffi/api/ffi.h` lives: $XLA_FFI_INCLUDE_DIR, jaxlib's copy when JAX is
+    installed, else the copy vendored by a mounted reference tree.  The headers are third-party
+    files and are only ever included from where they lie."""
+    cands = [os.environ.get("XLA_FFI_INCLUDE_DIR")]
+    try:
+        import jax.ffi  # type: ignore
+
+        cands.append(jax.ffi.include_dir())
+    except Exception:
+        pass
+    cands.append(os.path.join(os.environ.get("E3J_REFERENCE_ROOT", "/root/reference"), "lib", "e3j_ops"))
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "xla", "ffi", "api", "ffi.h")):
+            return c
+    return None
+
+
+def build_xla_handlers(force: bool = False) -> str | None:
+    """Compile the XLA FFI handler shim (csrc/xla_ffi_handlers.cc) against the C ABI library.
+    Returns None when no XLA FFI headers are available."""
+    inc = xla_ffi_include_dir()
+    if inc is None:
+        return XLA_LIB_PATH if os.path.exists(XLA_LIB_PATH) else None
+    src = os.path.join(CSRC, "xla_ffi_handlers.cc")
+    if not force and os.path.exists(XLA_LIB_PATH) and os.path.getmtime(XLA_LIB_PATH) >= max(
+        os.path.getmtime(src), os.path.getmtime(os.path.join(INCLUDE, "e3j_b200.h"))
+    ):
+        return XLA_LIB_PATH
+    build()
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, "-O2", "-std=c++17", "-x", "cu", "-Xcompiler", "-fPIC", "-shared", "-I", inc, "-o", XLA_LIB_PATH, src,
+           "-L", _HERE, "-le3j_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]  # fmt: skip
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode:
+        print(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libe3j_b200_xla.so")
+    return XLA_LIB_PATH
+
+
 def _declare(lib: ctypes.CDLL) -> None:
     c = ctypes
     vp, i32, i64 = c.c_void_p, c.c_int32, c.c_int64
@@ -97,6 +140,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_csr_transpose_workspace_bytes.argtypes = [i32, i64]
     lib.e3j_b200_csr_transpose.restype = c.c_int
     lib.e3j_b200_csr_transpose.argtypes = [vp, i64, i32, vp, vp, vp, c.c_size_t, vp]
+    lib.e3j_b200_csr_untranspose.restype = c.c_int
+    lib.e3j_b200_csr_untranspose.argtypes = [vp, vp, vp, i32, i64, vp, vp, vp]
     lib.e3j_b200_harmonics_fwd.restype = c.c_int
     lib.e3j_b200_harmonics_fwd.argtypes = [vp, vp, i32, i32, i32, vp, vp, i64, vp]
     lib.e3j_b200_harmonics_bwd.restype = c.c_int
@@ -125,6 +170,7 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_csr_ptr",
     "e3j_b200_csr_transpose_workspace_bytes",
     "e3j_b200_csr_transpose",
+    "e3j_b200_csr_untranspose",
     "e3j_b200_harmonics_fwd",
     "e3j_b200_harmonics_bwd",
 )

@@ -78,5 +78,28 @@ __global__ void __launch_bounds__(128) sort_segments_kernel(const int32_t *__res
     }
 }
 
+// Receiver-sorted edge list back from its sender-sorted view: for the p-th edge in sender
+// order (row a of `sender_ptr_t`, original position perm_t[p], receiver recv_t[p])
+// sender[perm_t[p]] = a and receiver[perm_t[p]] = recv_t[p].  Edges that appear in no row
+// keep the padding value the caller filled the outputs with.  One warp per sender row.
+__global__ void untranspose_kernel(const int32_t *__restrict__ sender_ptr_t, const int32_t *__restrict__ perm_t,
+                                   const int32_t *__restrict__ recv_t, int32_t N, int32_t *__restrict__ sender,
+                                   int32_t *__restrict__ receiver) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t a = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; a < N;
+         a += ((int64_t)gridDim.x * blockDim.x) >> 5) {
+        for (int32_t p = sender_ptr_t[a] + lane; p < sender_ptr_t[a + 1]; p += 32) {
+            const int32_t e = perm_t[p];
+            sender[e] = (int32_t)a;
+            receiver[e] = recv_t[p];
+        }
+    }
+}
+
+__global__ void fill_i32_kernel(int32_t *__restrict__ dst, int64_t n, int32_t value) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
+        dst[t] = value;
+}
+
 }  // namespace csr
 }  // namespace e3jb

@@ -374,6 +374,20 @@ int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t 
     return check_launch("csr_transpose", 0, stream);
 }
 
+int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t, const int32_t *recv_t, int32_t N,
+                             int64_t E, int32_t *sender, int32_t *receiver, e3j_b200_stream stream) {
+    if (N < 0 || E < 0 || !sender_ptr_t || (E > 0 && (!perm_t || !recv_t || !sender || !receiver)))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "bad CSR operands");
+    if (E == 0) return E3J_B200_OK;
+    const int grid = (int)std::min<int64_t>(ceil_div64(E, 256), 148 * 8);
+    csr::fill_i32_kernel<<<grid, 256, 0, stream>>>(sender, E, 0x7fffffff);
+    csr::fill_i32_kernel<<<grid, 256, 0, stream>>>(receiver, E, 0x7fffffff);
+    const int ugrid = (int)std::min<int64_t>(ceil_div64((int64_t)N * 32, 256), 148 * 8);
+    if (N > 0)
+        csr::untranspose_kernel<<<ugrid, 256, 0, stream>>>(sender_ptr_t, perm_t, recv_t, N, sender, receiver);
+    return check_launch("csr_untranspose", 0, stream);
+}
+
 // ---------------------------------------------------------------------------
 // harmonics of edge vectors
 // ---------------------------------------------------------------------------

@@ -188,6 +188,14 @@ int e3j_b200_csr_ptr(const int32_t *index, int64_t E, int32_t N, int32_t *ptr, e
 size_t e3j_b200_csr_transpose_workspace_bytes(int32_t N, int64_t E);
 int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t *sender_ptr_t, int32_t *perm_t,
                            void *workspace, size_t workspace_bytes, e3j_b200_stream stream);
+/*
+ * Inverse view, for a caller that only holds what the reference hands its backward
+ * kernel (lib/e3j_ops/ffi/e3j_ops.h:478-494: the sender CSR `sender_ptr_t`, the per-edge
+ * receivers in sender order `recv_t`, and `perm_t`): writes the receiver-sorted
+ * sender[E] and receiver[E]; edges found in no sender row get the padding index INT32_MAX.
+ */
+int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t, const int32_t *recv_t, int32_t N,
+                             int64_t E, int32_t *sender, int32_t *receiver, e3j_b200_stream stream);
 
 /*
  * Real harmonics of edge vectors, the producer of `y`, and their vector-Jacobian

@@ -52,3 +52,13 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.LibraryMissing):
         _lib.lib()
+
+
+def test_xla_handler_library_exports_the_two_targets():
+    path = _lib.build_xla_handlers()
+    if path is None:
+        pytest.skip("no XLA FFI headers available: handler shim not built")
+    _lib.lib()
+    handle = ctypes.CDLL(path)
+    for name in ("e3j_b200_xla_convolution", "e3j_b200_xla_convolution_bwd"):
+        assert hasattr(handle, name)
