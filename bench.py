@@ -342,7 +342,7 @@ def run_ours(args):
         "e2e": None if args.no_e2e else {"value": edges_all / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int((hx.numel() + hy.numel() + hs.numel()) * 4),
                 "d2h_bytes_per_step": int(h_dx.numel() * 4 + 4), "ms_per_step": e2e_ms},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": sum(plan.launches) * args.steps,
         "clocks": clocks,
     }  # fmt: skip
     if cpu is not None:
@@ -470,7 +470,7 @@ def run_ours_slab(args, world, rank, local, device):
             "e2e": None if args.no_e2e else {"value": edges_all / (mx[1].item() * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": int((hx.numel() + hy.numel() + hs.numel()) * 4),
                     "d2h_bytes_per_step": int(h_dx.numel() * 4 + 4), "ms_per_step": mx[1].item()},
-            "gpu_launches": args.steps * (2 + 3 + 2 * n_peers),
+            "gpu_launches": args.steps * (2 * plan.launches[0] + plan.launches[1] + 2 * n_peers),
             "clocks": clocks,
         }  # fmt: skip
         print(json.dumps(line))

@@ -118,6 +118,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_plan_destroy.argtypes = [vp]
     lib.e3j_b200_plan_variant.restype = c.c_int
     lib.e3j_b200_plan_variant.argtypes = [vp]
+    lib.e3j_b200_plan_launches.restype = c.c_int
+    lib.e3j_b200_plan_launches.argtypes = [vp, c.POINTER(c.c_int32), c.POINTER(c.c_int32)]
     lib.e3j_b200_conv_fwd.restype = c.c_int
     lib.e3j_b200_conv_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i64, i32, vp]
     lib.e3j_b200_conv_bwd_workspace_bytes.restype = c.c_size_t
@@ -158,6 +160,7 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_plan_create",
     "e3j_b200_plan_destroy",
     "e3j_b200_plan_variant",
+    "e3j_b200_plan_launches",
     "e3j_b200_conv_fwd",
     "e3j_b200_conv_bwd_workspace_bytes",
     "e3j_b200_conv_bwd",

@@ -168,6 +168,14 @@ void e3j_b200_plan_destroy(e3j_b200_plan *p) {
 
 int e3j_b200_plan_variant(const e3j_b200_plan *p) { return p ? p->variant : -1; }
 
+int e3j_b200_plan_launches(const e3j_b200_plan *p, int32_t *fwd, int32_t *bwd) {
+    if (!p || !fwd || !bwd) return set_error(E3J_B200_INVALID_ARGUMENT, "plan_launches: null argument");
+    const bool un = p->variant != E3J_B200_VARIANT_GENERIC;
+    *fwd = un ? p->un.fwd_launches : 1;
+    *bwd = (un ? p->un.dy_partials : 1) + 2;  // per-edge pass(es) + dy finish + dx reduction
+    return E3J_B200_OK;
+}
+
 // ---------------------------------------------------------------------------
 // generic launch geometry
 // ---------------------------------------------------------------------------

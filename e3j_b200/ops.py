@@ -68,6 +68,13 @@ class ConvPlan:
     def variant(self) -> int:
         return int(_lib.lib().e3j_b200_plan_variant(self.handle))
 
+    @property
+    def launches(self) -> tuple[int, int]:
+        """Kernels launched by one forward and by one backward call."""
+        f, b = ctypes.c_int32(), ctypes.c_int32()
+        _lib.check(_lib.lib().e3j_b200_plan_launches(self.handle, ctypes.byref(f), ctypes.byref(b)))
+        return f.value, b.value
+
     def __del__(self):
         try:
             if getattr(self, "handle", None):

@@ -87,6 +87,9 @@ int e3j_b200_plan_create(const void *coef_host, int32_t nnz, int32_t idx_bytes, 
                          e3j_b200_plan **plan);
 void e3j_b200_plan_destroy(e3j_b200_plan *plan);
 int e3j_b200_plan_variant(const e3j_b200_plan *plan);
+/* Kernels launched by one forward call and by one full backward call of this plan
+ * (the large variant runs one kernel per group of output paths). */
+int e3j_b200_plan_launches(const e3j_b200_plan *plan, int32_t *fwd, int32_t *bwd);
 
 /*
  * Forward: out[r, i, c] = sum_{e in segment r} sum_n val_n x[sender[e], j_n, c] y[e, k_n] s[e, l_n, c].
