@@ -55,6 +55,8 @@ def workload_name(config: int) -> str:
         2: "config2: N=25000 periodic cube, cutoff 5 A, x=0e+1o+2e+3o, y=lmax3, out l<=3, C=128, fwd+VJP",
         3: "config3: 1024 molecules of 10-40 atoms, padded to x128, x=0e+1o+2e+3o, C=128, fwd+VJP",
         0: "config0: N=512 open cube, cutoff 4.5 A, x=0e+1o, C=128, fwd+VJP",
+        4: "config4: N=1048576 periodic cube, cutoff 5 A, x=0e+1o+2e+3o, C=128, fwd+VJP (CPU sample drawn from the "
+           "config-2 cube: same irreps, density and cutoff)",
     }[config]
 
 
@@ -122,7 +124,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    res = time_cpu(args.config, max(1, args.steps), max(1, min(args.warmup, 2)))
+    # config 4 has the irreps, density and cutoff of config 2: the same bounded sample stands for it
+    cfg = 2 if args.config == 4 else args.config
+    res = time_cpu(cfg, max(1, args.steps), max(1, min(args.warmup, 2)))
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
@@ -198,8 +202,12 @@ def run_ours(args):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+        if args.config == 4:
+            return run_ours_config4(args, world, rank, local, device)
         if args.workload != "independent":
             return run_ours_slab(args, world, rank, local, device)
+    elif args.config == 4:
+        return run_ours_config4(args, world, rank, local, device)
 
     cfg = args.config
     conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
@@ -477,17 +485,196 @@ def run_ours_slab(args, world, rank, local, device):
     dist.destroy_process_group()
 
 
+def run_ours_config4(args, world, rank, local, device):
+    """Config 4: one periodic cube (default 1 048 576 nodes, ~55 M directed edges, l <= 3 hidden
+    layer) split into `world` slabs along x.  The per-edge scalars do not fit in memory, so
+    every rank runs its receivers in windows of `--window-edges` edges and evaluates the
+    radial MLP per window (again in the backward pass, where the window's ds is folded into
+    the MLP weight gradients at once).  Strong scaling: the graph is the same at every N."""
+    import torch
+    import torch.distributed as dist
+
+    from e3j_b200 import ops, problems
+    from e3j_b200.chunked import RadialProducer, WindowedConvOps
+    from e3j_b200.convolution import Convolution
+    from e3j_b200.halo import CudaRowOps, HaloConvolution
+    from e3j_b200.harmonics import Harmonics
+    from e3j_b200.partition import periodic_slab_part
+    from e3j_b200.radial import RadialMLP, bessel_envelope
+
+    cfg, cutoff = 2, 5.0  # irreps and cutoff of config 2
+    n_nodes = args.nodes or 1 << 20
+    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+                       avg_num_neighbors=30.0)  # fmt: skip
+    X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
+    box = (n_nodes / problems.DENSITY) ** (1.0 / 3.0)
+    pos = np.random.default_rng(0).uniform(0.0, box, size=(n_nodes, 3))
+    t_build = time.perf_counter()
+    part, vec = periodic_slab_part(rank, world, pos, box, cutoff, cell=cutoff / 2)
+    t_build = time.perf_counter() - t_build
+    plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
+    wops = WindowedConvOps(plan, args.window_edges)
+    halo = HaloConvolution(part, (X, Y, Z, S, C), device, wops, CudaRowOps)
+
+    gen = torch.Generator(device=device).manual_seed(1 + rank)
+    x_loc = torch.zeros((part.n_loc, X, C), device=device)
+    x_loc[: part.n_own] = torch.randn((part.n_own, X, C), generator=gen, device=device)
+    vec_d = torch.as_tensor(vec, dtype=torch.float32).to(device)
+    del vec
+    y = Harmonics(3, normalize=True).cuda(vec_d).contiguous()
+    rbf = bessel_envelope(torch.linalg.norm(vec_d, dim=1), cutoff, 8).contiguous()
+    del vec_d
+    mlp = RadialMLP.init(8, 64, S * C, 0)
+    prod = RadialProducer(rbf, torch.as_tensor(mlp.w1).to(device), torch.as_tensor(mlp.w2).to(device))
+    e_loc = int(y.shape[0])
+
+    out = torch.empty((part.n_own, Z, C), device=device)  # doubles as dm = 2 out (loss = sum out^2)
+    dx_loc, dy = torch.empty_like(x_loc), torch.empty_like(y)
+
+    def step():
+        prod.zero_grad()
+        halo.forward(x_loc, y, prod, out)
+        out.mul_(2.0)
+        halo.backward(x_loc, y, prod, out, dx_loc, dy, None)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n_warm = max(3, args.warmup)
+    for _ in range(n_warm):
+        step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wops.windows_run = 0
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = a.elapsed_time(b)
+    windows_per_step = wops.windows_run // max(args.steps, 1)
+
+    # one more step with the producer's share timed (events around its calls)
+    spans = []
+
+    class Timed:
+        def __init__(self, inner):
+            self.inner = inner
+
+        def _run(self, fn, *a):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(*a)
+            e1.record()
+            spans.append((e0, e1))
+
+        def forward(self, *a):
+            self._run(self.inner.forward, *a)
+
+        def backward(self, *a):
+            self._run(self.inner.backward, *a)
+
+    timed = Timed(prod)
+    a.record()
+    halo.forward(x_loc, y, timed, out)
+    out.mul_(2.0)
+    halo.backward(x_loc, y, timed, out, dx_loc, dy, None)
+    b.record()
+    barrier()
+    producer_ms = sum(p.elapsed_time(q) for p, q in spans)
+    one_step_ms = a.elapsed_time(b)
+
+    # end to end: node features and edge attributes in pinned host memory, copied in every step
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.no_e2e:
+        hx, hy, hr = (t.cpu().pin_memory() for t in (x_loc[: part.n_own], y, rbf))
+        h_loss = torch.empty((), dtype=torch.float32).pin_memory()
+        h_dx = torch.empty((part.n_own, X, C), dtype=torch.float32).pin_memory()
+        h2d, d2h = int((hx.numel() + hy.numel() + hr.numel()) * 4), int(h_dx.numel() * 4 + 4)
+
+        def e2e_step():
+            x_loc[: part.n_own].copy_(hx, non_blocking=True)
+            y.copy_(hy, non_blocking=True)
+            rbf.copy_(hr, non_blocking=True)
+            prod.zero_grad()
+            halo.forward(x_loc, y, prod, out)
+            loss = (out * out).sum()
+            out.mul_(2.0)
+            halo.backward(x_loc, y, prod, out, dx_loc, dy, None)
+            h_loss.copy_(loss, non_blocking=True)
+            h_dx.copy_(dx_loc[: part.n_own], non_blocking=True)
+
+        e2e_step()
+        barrier()
+        n_e2e = max(1, min(args.steps, 3))
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b) / n_e2e
+
+    stats = torch.tensor([ms_total, e2e_ms, float(e_loc), float(part.n_loc - part.n_own), producer_ms, one_step_ms,
+                          t_build, float(torch.cuda.max_memory_allocated(device))], device=device, dtype=torch.float64)  # fmt: skip
+    mx, sm = stats.clone(), stats.clone()
+    if world > 1:
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms_step = mx[0].item() / args.steps
+        edges_all = sm[2].item()
+        peak, peak_kind = load_peaks()
+        alg = algorithmic_bytes(edges_all, n_nodes, X, Y, Z, S, C)
+        conv_ms = max(mx[5].item() - mx[4].item(), 1e-9)
+        n_peers = len(halo.peers)
+        fwd_l, bwd_l = plan.launches
+        line = {
+            "metric": METRIC, "value": edges_all / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": n_warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config4: %d nodes in a periodic cube (density 0.1 / A^3, cutoff 5 A), x = y = out filter "
+                       "= 0e+1o+2e+3o, C=128, slabs along x, fwd+VJP with halo exchange; scalars from the radial MLP per "
+                       "window of <= %d edges (evaluated twice per step), MLP weight gradients included" % (n_nodes, args.window_edges),
+                       "nodes_total": n_nodes, "edges_total": int(edges_all), "halo_rows_total": int(sm[3].item()),
+                       "windows_per_step_rank0": windows_per_step, "channels": C, "variant": plan.variant,
+                       "parallelism": f"slab{world} + p2p halo (NCCL)" if world > 1 else "1 GPU, windows",
+                       "node_order": "Z-order curve, 2.5 A cells", "graph_build_s_max": mx[6].item(),
+                       "max_memory_allocated_gb_max": mx[7].item() / 1e9,
+                       "l2": "inputs larger than L2 (a window's s and ds are %.1f GB each)" % (args.window_edges * S * C * 4 / 1e9)},
+            "roofline": {"bound": "hbm", "kernel": "convolution kernels of one step (all windows), slowest rank",
+                         "achieved": sum(alg.values()) / world / (conv_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": sum(alg.values()) / world / (conv_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                         "peak_source": peak_kind, "conv_ms": conv_ms, "producer_ms": mx[4].item(),
+                         "note": "conv_ms = step time minus the time inside the radial-MLP producer (events around its "
+                                 "calls, one instrumented step); algorithmic bytes as if s and ds were streamed once"},
+            "e2e": None if args.no_e2e else {"value": edges_all / (mx[1].item() * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": mx[1].item()},
+            "gpu_launches": args.steps * (windows_per_step * (fwd_l + bwd_l) + 2 * n_peers),
+            "clocks": clocks,
+        }  # fmt: skip
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3])
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="slab", choices=["slab", "independent"],
                     help="N > 1: one partitioned graph with halo exchange (default) or one graph per rank")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--window-edges", type=int, default=1 << 20, help="config 4: edges per window")
     ap.add_argument("--nodes", type=int, default=None, help="override the node count (small profiling cases)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -132,6 +132,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_conv_fwd_rect.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, vp]
     lib.e3j_b200_conv_bwd_rect.restype = c.c_int
     lib.e3j_b200_conv_bwd_rect.argtypes = [vp] * 13 + [c.c_size_t, i32, i32, i64, i32, vp, i32]
+    lib.e3j_b200_conv_fwd_window.restype = c.c_int
+    lib.e3j_b200_conv_fwd_window.argtypes = [vp] * 7 + [i32, i32, i64, i64, i32, vp]
+    lib.e3j_b200_conv_bwd_window.restype = c.c_int
+    lib.e3j_b200_conv_bwd_window.argtypes = [vp] * 13 + [c.c_size_t, i32, i32, i64, i64, i32, i32, vp]
     lib.e3j_b200_rows_gather.restype = c.c_int
     lib.e3j_b200_rows_gather.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.e3j_b200_rows_add.restype = c.c_int
@@ -168,6 +172,8 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd_static",
     "e3j_b200_conv_fwd_rect",
     "e3j_b200_conv_bwd_rect",
+    "e3j_b200_conv_fwd_window",
+    "e3j_b200_conv_bwd_window",
     "e3j_b200_rows_gather",
     "e3j_b200_rows_add",
     "e3j_b200_csr_ptr",

@@ -174,11 +174,12 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
 // (E * dy_row floats each), dy = their sum in buffer order; (b) edges at or beyond
 // receiver_ptr[N] belong to no receiver: their dy, ds and dx message are exact zeros
 // (lib/e3j_ops/cuda/convolution/bwd.cuh:308-319).
-__global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t E,
-                                  float *__restrict__ dxm, int64_t dxm_row, float *__restrict__ dy,
-                                  int64_t dy_row, float *__restrict__ ds, int64_t ds_row,
-                                  const float *__restrict__ dy_part, int nparts) {
-    const int64_t first = min((int64_t)receiver_ptr[N], E);
+// The buffers hold the edge window [e_begin, e_begin + E) of the CSR (e_begin = 0: all of it).
+__global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t e_begin,
+                                  int64_t E, float *__restrict__ dxm, int64_t dxm_row,
+                                  float *__restrict__ dy, int64_t dy_row, float *__restrict__ ds,
+                                  int64_t ds_row, const float *__restrict__ dy_part, int nparts) {
+    const int64_t first = max((int64_t)0, min((int64_t)receiver_ptr[N] - e_begin, E));
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     if (nparts > 1) {
@@ -273,6 +274,72 @@ __global__ void rows_add_kernel(float4 *__restrict__ dst, const int64_t *__restr
         *d = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
     }
 }
+
+// ---------------------------------------------------------------------------
+// backward, pass 2 for an edge window: the messages of the edges [e0, e1) only (dxm row 0
+// is edge e0).  A sender's segment of perm_t lists its edges in ascending order (the
+// transposition is stable), so the window's part of it is contiguous; the lanes of the
+// warp count the entries below e0 and below e1 to find it.  With `accumulate` the sum
+// continues from the row already in dx (same order of additions as one pass over the
+// whole segment) and rows with no edge in the window are left alone; without it they
+// are set to zero.  One warp per sender row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dx_reduce_window_kernel(const float *__restrict__ dxm,
+                                                               const int32_t *__restrict__ sender_ptr_t,
+                                                               const int32_t *__restrict__ perm_t,
+                                                               float *__restrict__ dx, int32_t N, int64_t XC,
+                                                               int64_t e0, int64_t e1, int accumulate) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const bool vec4 = (XC & 3) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(dxm) & 15) == 0;
+    for (int64_t a = warp; a < N; a += nwarps) {
+        const int32_t p0 = sender_ptr_t[a], p1 = sender_ptr_t[a + 1];
+        int below0 = 0, below1 = 0;
+        for (int32_t p = p0 + lane; p < p1; p += 32) {
+            const int64_t e = perm_t[p];
+            below0 += e < e0;
+            below1 += e < e1;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            below0 += __shfl_xor_sync(0xffffffffu, below0, o);
+            below1 += __shfl_xor_sync(0xffffffffu, below1, o);
+        }
+        const int32_t q0 = p0 + below0, q1 = p0 + below1;
+        if (q0 == q1 && accumulate) continue;
+        float *row = dx + a * XC;
+        if (vec4) {
+            for (int64_t v = lane; v < XC / 4; v += 32) {
+                float4 acc = accumulate ? reinterpret_cast<const float4 *>(row)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+                int32_t q = q0;
+                for (; q + 4 <= q1; q += 4) {
+                    float4 t[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        t[u] = reinterpret_cast<const float4 *>(dxm + ((int64_t)perm_t[q + u] - e0) * XC)[v];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w;
+                    }
+                }
+                for (; q < q1; q++) {
+                    const float4 t = reinterpret_cast<const float4 *>(dxm + ((int64_t)perm_t[q] - e0) * XC)[v];
+                    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+                }
+                reinterpret_cast<float4 *>(row)[v] = acc;
+            }
+        } else {
+            for (int64_t v = lane; v < XC; v += 32) {
+                float acc = accumulate ? row[v] : 0.f;
+                for (int32_t q = q0; q < q1; q++) acc += dxm[((int64_t)perm_t[q] - e0) * XC + v];
+                row[v] = acc;
+            }
+        }
+    }
+}
+
 
 }  // namespace generic
 }  // namespace e3jb

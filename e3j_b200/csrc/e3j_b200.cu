@@ -276,11 +276,59 @@ int e3j_b200_conv_bwd_phases(const e3j_b200_plan *p, const float *x, const float
                                   workspace, workspace_bytes, N, N, E, debug, stream, phases);
 }
 
+// Backward over the edge window [e0, e0 + E) of the CSR: y, s, sender, dy, ds and the
+// workspace hold the window's edges only (first row: edge e0); receiver_ptr holds absolute
+// edge indices.  The per-edge kernels index by absolute edge, so they get the bases moved
+// back by e0 rows; window < 0 means the whole graph (e0 = 0, dx overwritten).
+static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                    const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                    const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                    float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                    int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases, int64_t e0,
+                    int window, int accumulate);
+
 int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
                            const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
                            const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
                            float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
                            int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases) {
+    return bwd_core(p, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, workspace,
+                    workspace_bytes, N, NS, E, debug, stream, phases, 0, 0, 0);
+}
+
+int e3j_b200_conv_bwd_window(const e3j_b200_plan *p, const float *x, const float *y_w, const float *s_w,
+                             const float *dm_w, const int32_t *sender_w, const int32_t *receiver_ptr_w,
+                             const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy_w,
+                             float *ds_w, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                             int64_t e0, int64_t E, int32_t accumulate, int32_t debug,
+                             e3j_b200_stream stream) {
+    if (e0 < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative window start");
+    return bwd_core(p, x, y_w, s_w, dm_w, sender_w, receiver_ptr_w, sender_ptr_t, perm_t, dx, dy_w, ds_w,
+                    workspace, workspace_bytes, N, NS, E, debug, stream, E3J_B200_BWD_ALL, e0, 1,
+                    accumulate != 0);
+}
+
+int e3j_b200_conv_fwd_window(const e3j_b200_plan *p, const float *x, const float *y_w, const float *s_w,
+                             const int32_t *sender_w, const int32_t *receiver_ptr_w, float *out_w,
+                             int32_t N, int32_t NS, int64_t e0, int64_t E, int32_t debug,
+                             e3j_b200_stream stream) {
+    if (e0 < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative window start");
+    int rc = check_common(p, N, E);
+    if (rc) return rc;
+    if (E > 0 && (!y_w || !s_w || !sender_w)) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    const Dims &d = p->d;
+    return e3j_b200_conv_fwd_rect(p, x, y_w ? y_w - e0 * d.Y : nullptr,
+                                  s_w ? s_w - e0 * (int64_t)d.S * d.C : nullptr,
+                                  sender_w ? sender_w - e0 : nullptr, receiver_ptr_w, out_w, N, NS, e0 + E,
+                                  debug, stream);
+}
+
+static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                    const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
+                    const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                    float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                    int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases, int64_t e0,
+                    int window, int accumulate) {
     int rc = check_common(p, N, E);
     if (rc) return rc;
     if (NS < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative sender count");
@@ -299,10 +347,15 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *
                                                             ((size_t)E * d.X * d.C * sizeof(float) + 255) / 256 * 256)
                                 : dy;
 
+    // bases as the per-edge kernels see them: row of (absolute) edge 0
+    const float *y0 = y ? y - e0 * d.Y : nullptr, *s0 = s ? s - e0 * (int64_t)d.S * d.C : nullptr;
+    const int32_t *sender0 = sender ? sender - e0 : nullptr;
+    float *dxm0 = dxm - e0 * (int64_t)d.X * d.C, *ds0 = ds ? ds - e0 * (int64_t)d.S * d.C : nullptr;
+    float *dy0 = dy ? dy - e0 * d.Y : nullptr, *dy_part0 = dy_part ? dy_part - e0 * d.Y : nullptr;
     if (E > 0 && (phases & E3J_B200_BWD_EDGES)) {
         if (p->variant != E3J_B200_VARIANT_GENERIC) {
-            rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y, s, dm, sender,
-                                            receiver_ptr, dxm, dy_part, ds, N, NS, E, debug, stream);
+            rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y0, s0, dm, sender0,
+                                            receiver_ptr, dxm0, dy_part0, ds0, N, NS, E, debug, stream);
             if (rc) return rc;
         } else {
             const GenericGeometry g = generic_geometry(p);
@@ -319,20 +372,26 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *
             const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
             DeviceTable t{p->d_val, p->d_idx, p->nnz};
             generic::conv_bwd_edges_kernel<<<grid, g.block, smem, stream>>>(
-                t, g.table_in_smem, x, y, s, dm, sender, receiver_ptr, dxm, dy, ds, N, NS, d);
+                t, g.table_in_smem, x, y0, s0, dm, sender0, receiver_ptr, dxm0, dy0, ds0, N, NS, d);
             rc = check_launch("convolution_bwd (edges)", debug, stream);
             if (rc) return rc;
         }
     }
     if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
         generic::bwd_finish_kernel<<<p->lim.sm_count * 8, 256, 0, stream>>>(
-            receiver_ptr, N, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
+            receiver_ptr, N, e0, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
         rc = check_launch("convolution_bwd (tail)", debug, stream);
         if (rc) return rc;
     }
     if (!(phases & E3J_B200_BWD_DX)) return E3J_B200_OK;
     const int64_t XC = (int64_t)d.X * d.C;
     if (NS == 0) return E3J_B200_OK;
+    if (window) {
+        const int wgrid = (int)std::min<int64_t>(ceil_div64(NS, 8), (int64_t)p->lim.sm_count * 8);
+        generic::dx_reduce_window_kernel<<<wgrid, 256, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC, e0,
+                                                                    e0 + E, accumulate);
+        return check_launch("convolution_bwd (dx, window)", debug, stream);
+    }
     const int grid = (int)std::min<int64_t>(NS, (int64_t)p->lim.sm_count * 16);
     const bool vec4 = XC % 4 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
     const int threads = (int)std::min<int64_t>(256, std::max<int64_t>(32, (XC / (vec4 ? 4 : 1) + 31) / 32 * 32));

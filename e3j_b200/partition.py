@@ -52,12 +52,34 @@ def slab_of(x: np.ndarray, lo: float, hi: float, world: int) -> np.ndarray:
     return np.clip(np.floor((x - lo) / w).astype(np.int64), 0, world - 1)
 
 
+def morton_order(positions: np.ndarray, cell: float) -> np.ndarray:
+    """Permutation sorting points along the Z-order curve of a grid of `cell`-sized boxes
+    (ties broken by index).  Consecutive points are close in space, so consecutive
+    receivers gather largely the same sender rows and those stay in L2."""
+    q = np.floor((positions - positions.min(axis=0)) / cell).astype(np.uint64)
+    assert q.max(initial=0) < (1 << 21)
+    code = np.zeros(q.shape[0], np.uint64)
+    for bit in range(21):
+        for dim in range(3):
+            code |= ((q[:, dim] >> np.uint64(bit)) & np.uint64(1)) << np.uint64(3 * bit + dim)
+    return np.lexsort((np.arange(q.shape[0]), code))
+
+
+def _ordered(ids: np.ndarray, positions: np.ndarray, cell: float | None) -> np.ndarray:
+    """`ids` ascending, or along the Z-order curve of their positions when `cell` is given."""
+    if cell is None or ids.size == 0:
+        return ids
+    return ids[morton_order(positions[ids], cell)]
+
+
 def partition_slabs(positions: np.ndarray, sender: np.ndarray, receiver: np.ndarray, world: int,
-                    lo: float | None = None, hi: float | None = None) -> list[SlabPart]:  # fmt: skip
+                    lo: float | None = None, hi: float | None = None, cell: float | None = None) -> list[SlabPart]:  # fmt: skip
     """Split a receiver-sorted global edge list into per-rank local graphs.
 
     `sender` / `receiver` are global ids of real edges (no padding).  Returns one
-    :class:`SlabPart` per rank with mutually consistent exchange plans.
+    :class:`SlabPart` per rank with mutually consistent exchange plans.  With `cell`
+    the interior and the boundary nodes are each numbered along a Z-order curve
+    (:func:`morton_order`) instead of by ascending global id.
     """
     n = positions.shape[0]
     lo = float(positions[:, 0].min()) if lo is None else lo
@@ -76,8 +98,8 @@ def partition_slabs(positions: np.ndarray, sender: np.ndarray, receiver: np.ndar
         # a receiver is "boundary" if any of its senders is foreign
         is_boundary = np.zeros(n, bool)
         is_boundary[rcv_g[foreign]] = True
-        interior = owned[~is_boundary[owned]]
-        boundary = owned[is_boundary[owned]]
+        interior = _ordered(owned[~is_boundary[owned]], positions, cell)
+        boundary = _ordered(owned[is_boundary[owned]], positions, cell)
         halo = np.unique(snd_g[foreign])
         halo = halo[np.lexsort((halo, owner[halo]))]  # grouped by owning peer, ascending id inside
         gids = np.concatenate([interior, boundary, halo])
@@ -122,3 +144,74 @@ def elongated_box_graph(world: int, nodes_per_slab: int, cutoff: float, density:
     snd, rcv, vec = radius_graph(pos, cutoff, None)
     g = Graph(n, pos, snd, rcv, vec, None, n, snd.shape[0], {"side": side, "cutoff": cutoff, "world": world, "seed": seed})
     return g, 0.0, side * world
+
+
+def periodic_slab_part(rank: int, world: int, positions: np.ndarray, box: float, cutoff: float,
+                       cell: float | None = None):  # fmt: skip
+    """The :class:`SlabPart` of one rank of a fully periodic cubic box, built from the
+    positions alone: only the rank's slab and the `cutoff`-wide layers next to its two
+    faces are searched, so a million-node graph never exists in one piece.  Same
+    numbering, edge order and exchange plan as ``partition_slabs`` gives for the global
+    radius graph (`edge_ids` is left empty).  Returns ``(part, vectors)`` with
+    ``vectors[e] = pos[receiver] - pos[sender]`` (minimum image) of the local edges.
+    """
+    from scipy.spatial import cKDTree
+
+    n = positions.shape[0]
+    pos = np.mod(positions, box)
+    pos[pos >= box] -= box
+    owner = slab_of(pos[:, 0], 0.0, box, world)
+    width = box / world
+    if world > 1 and width + 2 * cutoff >= box:
+        raise ValueError("slabs are too thin for the periodic box: a halo would wrap onto its own slab")
+    if world == 1:
+        cand = np.arange(n)
+        tree = cKDTree(pos, boxsize=box)
+    else:
+        # x relative to the slab's lower face, unwrapped: [-cutoff, width + cutoff)
+        xr = np.mod(pos[:, 0] - rank * width, box)
+        xr[xr >= box] -= box
+        xu = np.where(xr >= box - cutoff, xr - box, xr)
+        mine = owner == rank
+        cand = np.nonzero(mine | ((xu >= -cutoff) & (xu < width + cutoff)))[0]
+        span = width + 4 * cutoff + 2.0  # wider than the candidates' extent + cutoff: no wrap along x
+        pts = np.stack([np.clip(xu[cand] + cutoff + 1.0, 0.0, np.nextafter(span, 0.0)), pos[cand, 1], pos[cand, 2]], axis=1)
+        tree = cKDTree(pts, boxsize=[span, box, box])
+    pairs = tree.query_pairs(cutoff, output_type="ndarray")
+    a, b = cand[pairs[:, 0]], cand[pairs[:, 1]]
+    snd = np.concatenate([a, b])
+    rcv = np.concatenate([b, a])
+    keep = owner[rcv] == rank
+    snd_g, rcv_g = snd[keep], rcv[keep]
+    foreign = owner[snd_g] != rank
+    owned = np.nonzero(owner == rank)[0]
+    is_boundary = np.zeros(n, bool)
+    is_boundary[rcv_g[foreign]] = True
+    interior = _ordered(owned[~is_boundary[owned]], positions, cell)
+    boundary = _ordered(owned[is_boundary[owned]], positions, cell)
+    halo = np.unique(snd_g[foreign])
+    halo = halo[np.lexsort((halo, owner[halo]))]
+    gids = np.concatenate([interior, boundary, halo])
+    local = np.full(n, -1, np.int64)
+    local[gids] = np.arange(gids.size)
+    order = np.lexsort((snd_g, local[rcv_g]))  # local receiver major, global sender minor
+    snd_g, rcv_g = snd_g[order], rcv_g[order]
+    part = SlabPart(rank, world, interior.size, owned.size, gids.size, gids, local[snd_g].astype(np.int32),
+                    local[rcv_g].astype(np.int32), np.empty(0, np.int64))  # fmt: skip
+    start = owned.size
+    for p in np.unique(owner[halo]):
+        cnt = int((owner[halo] == p).sum())
+        part.recv_slice[int(p)] = (start, start + cnt)
+        start += cnt
+    # what each peer needs from this rank: the owned senders of the edges into that peer's slab,
+    # i.e. the owned ends of the cross pairs found above, in ascending global id
+    cross = owner[rcv] != rank
+    cs, cr = snd[cross], rcv[cross]
+    own_end = owner[cs] == rank
+    cs, cr = cs[own_end], cr[own_end]
+    for p in np.unique(owner[cr]):
+        ids = np.unique(cs[owner[cr] == p])
+        part.send_rows[int(p)] = local[ids]
+    vec = pos[rcv_g] - pos[snd_g]
+    vec -= box * np.round(vec / box)
+    return part, vec

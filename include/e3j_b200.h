@@ -166,6 +166,34 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *plan, const float *x, const floa
                            int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases);
 
 /*
+ * Edge windows (no counterpart in the reference): a graph whose per-edge operands do
+ * not fit in memory at once is run as consecutive receiver ranges, the per-edge scalars
+ * of each range being produced just before use.  A window is the receivers
+ * [r0, r0 + N) of the CSR and their edges [e0, e0 + E), e0 = receiver_ptr[r0]:
+ *   receiver_ptr_w = receiver_ptr + r0 (N + 1 entries, still absolute edge indices),
+ *   y_w, s_w, sender_w, dy_w, ds_w: the window's rows only (row 0 is edge e0),
+ *   out_w, dm_w: the window's receivers only (row 0 is receiver r0),
+ *   x, dx (NS rows), sender_ptr_t, perm_t: of the whole graph, as for the _rect calls.
+ * The backward adds the window's messages to dx when `accumulate` is non-zero (rows of
+ * senders without an edge in the window are left untouched) and overwrites dx
+ * (zeros for such senders) otherwise: running the windows in ascending order with
+ * accumulate = 0 for the first one performs, for every sender, exactly the additions of
+ * the one-pass backward in the same order, so dx is bitwise the same.
+ * Workspace: e3j_b200_conv_bwd_workspace_bytes(plan, N, E) for the window's E.
+ */
+int e3j_b200_conv_fwd_window(const e3j_b200_plan *plan, const float *x, const float *y_w, const float *s_w,
+                             const int32_t *sender_w, const int32_t *receiver_ptr_w, float *out_w,
+                             int32_t N, int32_t NS, int64_t e0, int64_t E, int32_t debug,
+                             e3j_b200_stream stream);
+
+int e3j_b200_conv_bwd_window(const e3j_b200_plan *plan, const float *x, const float *y_w, const float *s_w,
+                             const float *dm_w, const int32_t *sender_w, const int32_t *receiver_ptr_w,
+                             const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy_w,
+                             float *ds_w, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                             int64_t e0, int64_t E, int32_t accumulate, int32_t debug,
+                             e3j_b200_stream stream);
+
+/*
  * Halo packing helpers of the partitioned mode: dst[i, :] = src[idx[i], :] and
  * dst[idx[i], :] += src[i, :] for rows of `row_floats` floats (a multiple of 4,
  * buffers 16-byte aligned).  `idx` int64[n_rows] must be duplicate-free for
