@@ -525,7 +525,8 @@ def run_ours_config4(args, world, rank, local, device):
     rbf = bessel_envelope(torch.linalg.norm(vec_d, dim=1), cutoff, 8).contiguous()
     del vec_d
     mlp = RadialMLP.init(8, 64, S * C, 0)
-    prod = RadialProducer(rbf, torch.as_tensor(mlp.w1).to(device), torch.as_tensor(mlp.w2).to(device))
+    prod = RadialProducer(rbf, torch.as_tensor(mlp.w1).to(device), torch.as_tensor(mlp.w2).to(device),
+                          precision=args.producer)
     e_loc = int(y.shape[0])
 
     out = torch.empty((part.n_own, Z, C), device=device)  # doubles as dm = 2 out (loss = sum out^2)
@@ -581,6 +582,7 @@ def run_ours_config4(args, world, rank, local, device):
             self._run(self.inner.backward, *a)
 
     timed = Timed(prod)
+    barrier()  # rank 0 has just stopped its clock sampler: do not let the others wait for its halo rows
     a.record()
     halo.forward(x_loc, y, timed, out)
     out.mul_(2.0)
@@ -604,7 +606,7 @@ def run_ours_config4(args, world, rank, local, device):
             rbf.copy_(hr, non_blocking=True)
             prod.zero_grad()
             halo.forward(x_loc, y, prod, out)
-            loss = (out * out).sum()
+            loss = torch.linalg.vector_norm(out).square()  # sum of squares without a temporary of the size of out
             out.mul_(2.0)
             halo.backward(x_loc, y, prod, out, dx_loc, dy, None)
             h_loss.copy_(loss, non_blocking=True)
@@ -642,7 +644,7 @@ def run_ours_config4(args, world, rank, local, device):
                        "= 0e+1o+2e+3o, C=128, slabs along x, fwd+VJP with halo exchange; scalars from the radial MLP per "
                        "window of <= %d edges (evaluated twice per step), MLP weight gradients included" % (n_nodes, args.window_edges),
                        "nodes_total": n_nodes, "edges_total": int(edges_all), "halo_rows_total": int(sm[3].item()),
-                       "windows_per_step_rank0": windows_per_step, "channels": C, "variant": plan.variant,
+                       "windows_per_step_rank0": windows_per_step, "producer": args.producer, "channels": C, "variant": plan.variant,
                        "parallelism": f"slab{world} + p2p halo (NCCL)" if world > 1 else "1 GPU, windows",
                        "node_order": "Z-order curve, 2.5 A cells", "graph_build_s_max": mx[6].item(),
                        "max_memory_allocated_gb_max": mx[7].item() / 1e9,
@@ -674,6 +676,8 @@ def main():
                     help="N > 1: one partitioned graph with halo exchange (default) or one graph per rank")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
+                    help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
     ap.add_argument("--window-edges", type=int, default=1 << 20, help="config 4: edges per window")
     ap.add_argument("--nodes", type=int, default=None, help="override the node count (small profiling cases)")
     args = ap.parse_args()

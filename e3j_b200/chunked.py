@@ -44,18 +44,36 @@ def plan_windows(receiver_ptr: np.ndarray, r_lo: int, r_hi: int, max_edges: int)
     return out
 
 
+def split_tf32(t: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """t = hi + lo exactly, with hi holding the top 10 mantissa bits (exact in TF32)."""
+    hi = (t.view(torch.int32) & -8192).view(torch.float32)
+    return hi, t - hi
+
+
 class RadialProducer:
-    """``s = radial MLP(enveloped Bessel basis)`` evaluated per window (fp32 matrix products),
-    and its parameter gradients accumulated window by window.
+    """``s = radial MLP(enveloped Bessel basis)`` evaluated per window, and its parameter
+    gradients accumulated window by window.
 
     rbf: (E, B) basis values of every local edge; w1 (B, H), w2 (H, S * C).
+
+    `precision`: "fp32" evaluates the wide last layer as one fp32 matrix product;
+    "tf32x3" evaluates it on the tensor cores as h_hi W_hi + h_hi W_lo + h_lo W_hi, the
+    three products being one TF32 product over a three times longer inner dimension
+    ([h_hi, h_hi, h_lo] [W_hi; W_lo; W_hi]) with fp32 accumulation; the dropped lo x lo
+    term and the rounding of the lo parts are of relative size 2^-20.  The backward
+    products are fp32 in both modes.
     """
 
-    def __init__(self, rbf: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor):
-        self.rbf, self.w1, self.w2 = rbf, w1, w2
+    def __init__(self, rbf: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, precision: str = "fp32"):
+        if precision not in ("fp32", "tf32x3"):
+            raise ValueError(f"unknown precision {precision!r}")
+        self.rbf, self.w1, self.w2, self.precision = rbf, w1, w2, precision
         self.a1 = 1.0 / math.sqrt(w1.shape[0])
         self.a2 = 1.0 / math.sqrt(w2.shape[0])
         self.w2s = (w2 * self.a2).contiguous()
+        if precision == "tf32x3":
+            hi, lo = split_tf32(self.w2s)
+            self.w2s3 = torch.cat([hi, lo, hi], dim=0).contiguous()
         self.dw1 = torch.zeros_like(w1)
         self.dw2 = torch.zeros_like(w2)
 
@@ -70,7 +88,17 @@ class RadialProducer:
     def forward(self, e0: int, e1: int, s_w: torch.Tensor) -> None:
         """Fills `s_w` (e1 - e0, S, C)."""
         _, h = self._hidden(e0, e1)
-        torch.matmul(h, self.w2s, out=s_w.view(e1 - e0, -1))
+        if self.precision == "fp32":
+            torch.matmul(h, self.w2s, out=s_w.view(e1 - e0, -1))
+            return
+        hi, lo = split_tf32(h)
+        h3 = torch.cat([hi, hi, lo], dim=1)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            torch.matmul(h3, self.w2s3, out=s_w.view(e1 - e0, -1))
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
 
     def backward(self, e0: int, e1: int, ds_w: torch.Tensor) -> None:
         """Adds this window's contribution to dw1, dw2."""

@@ -195,3 +195,29 @@ def test_two_periodic_slabs_with_windows_and_radial_producer():
         assert_close(dx_locs[p.rank][: p.n_own].cpu().numpy(), dx_g[p.global_ids[: p.n_own]], what=f"dx rank {p.rank}")
     for got, want, name in ((dw1, dw1_g, "dw1"), (dw2, dw2_g, "dw2")):
         assert np.abs(got - want).max() <= 2e-4 * np.abs(want).max(), name
+
+
+@pytest.mark.gpu
+def test_split_tf32_product_of_the_radial_producer():
+    """The tensor-core evaluation of the wide layer stays within 3e-6 of the layer's scale."""
+    from e3j_b200.chunked import RadialProducer, split_tf32
+
+    dev = torch.device(DEV)
+    rng = np.random.default_rng(2)
+    e, S, C = 20000, 23, 128
+    r = rng.uniform(0.8, 4.99, e)
+    rbf = bessel_envelope_np(r, 5.0, 8).astype(np.float32)
+    mlp = RadialMLP.init(8, 64, S * C, seed=3)
+    want = mlp.forward_np(rbf, np.float64)
+    t = torch.from_numpy(rng.standard_normal(1000).astype(np.float32)).to(dev)
+    hi, lo = split_tf32(t)
+    assert torch.equal(hi + lo, t) and bool(((hi.view(torch.int32) & 8191) == 0).all())
+    errs = {}
+    for prec in ("fp32", "tf32x3"):
+        prod = RadialProducer(torch.from_numpy(rbf).to(dev), torch.from_numpy(mlp.w1).to(dev),
+                              torch.from_numpy(mlp.w2).to(dev), precision=prec)  # fmt: skip
+        s = torch.empty((e, S, C), device=dev)
+        prod.forward(0, e, s)
+        errs[prec] = float(np.abs(s.cpu().numpy().reshape(e, -1) - want).max() / np.abs(want).max())
+    assert errs["fp32"] < 1e-6 and errs["tf32x3"] < 3e-6, errs
+    assert not torch.backends.cuda.matmul.allow_tf32
