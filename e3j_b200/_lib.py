@@ -185,6 +185,20 @@ EXPORTED_SYMBOLS = (
 )
 
 
+_xla_lib = None
+
+
+def xla_lib() -> ctypes.CDLL:
+    """The XLA FFI handler library (`e3j_b200_xla_convolution`, `e3j_b200_xla_convolution_bwd`)."""
+    global _xla_lib
+    if _xla_lib is None:
+        if not os.path.exists(XLA_LIB_PATH):
+            raise LibraryMissing(f"{XLA_LIB_PATH} is missing: build it with e3j_b200._lib.build_xla_handlers()")
+        lib()  # the handlers link against the C ABI library next to them
+        _xla_lib = ctypes.CDLL(XLA_LIB_PATH)
+    return _xla_lib
+
+
 def lib() -> ctypes.CDLL:
     """Return the loaded library; raise if it has not been built."""
     global _lib

@@ -1,0 +1,60 @@
+"""Stand-in for the reference's compiled ``e3j_ops`` module (lib/e3j_ops/ffi/e3j_ops.cpp:79-99).
+
+``e3j.ops`` imports ``e3j_ops`` and registers every entry of ``get_registrations()`` as an
+XLA FFI target for platform "CUDA" (src/e3j/ops/__init__.py:15-24).  This module offers the
+same three functions on top of ``libe3j_b200_xla.so``; putting ``e3j_b200/shim`` (which holds
+a one-line ``e3j_ops.py`` re-exporting this module) on ``PYTHONPATH`` makes the unmodified
+e3j Python pick up the B200 kernels for the two convolution targets.  The standalone
+``tensor_product`` / ``tensor_product_bwd`` / ``scatter_add_1`` targets of the reference are
+not provided: the fused convolution path does not call them.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+from . import _lib
+
+TARGETS = ("convolution", "convolution_bwd")
+_CAPSULE_NAME = b"xla._CUSTOM_CALL_TARGET"  # the name jax.ffi.pycapsule gives its capsules
+_IDX_DTYPES = ("uint8", "int32")
+_VAL_DTYPES = ("float32", "float16", "float64")
+# Registers per thread the reference's launch heuristics are told about.  They only size
+# `coef_ranges`, which the handlers of this library accept and ignore.
+_NOMINAL_REGISTERS = 64
+
+
+def _capsule(address: int):
+    new = ctypes.pythonapi.PyCapsule_New
+    new.restype = ctypes.py_object
+    new.argtypes = (ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p)
+    return new(address, _CAPSULE_NAME, None)
+
+
+def handler_address(name: str) -> int:
+    """Address of the ``XLA_FFI_Error *(*)(XLA_FFI_CallFrame *)`` symbol of a target."""
+    if name not in TARGETS:
+        raise KeyError(name)
+    fn = getattr(_lib.xla_lib(), f"e3j_b200_xla_{name}")
+    return ctypes.cast(fn, ctypes.c_void_p).value
+
+
+def get_registrations() -> dict:
+    """``{target name: PyCapsule of its handler}`` as ``e3j_ops.get_registrations()``."""
+    return {name: _capsule(handler_address(name)) for name in TARGETS}
+
+
+def get_device_properties() -> dict:
+    """Same seven keys as the reference (lib/e3j_ops/ffi/e3j_ops.cpp:30-42)."""
+    from .ops import get_device_properties as props
+
+    return props()
+
+
+def get_kernel_registers(kernel: str, idx_dtype: str, val_dtype: str, N: int) -> int:
+    """Argument checks of the reference (lib/e3j_ops/ffi/e3j_ops.cpp:48-77); the value is nominal."""
+    if idx_dtype not in _IDX_DTYPES or val_dtype not in _VAL_DTYPES:
+        raise ValueError("get_kernel_registers: unsupported (idx_dtype, val_dtype) pair")
+    if kernel not in TARGETS:
+        raise ValueError(f"get_kernel_registers: unsupported kernel '{kernel}'")
+    return _NOMINAL_REGISTERS

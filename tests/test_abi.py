@@ -62,3 +62,32 @@ def test_xla_handler_library_exports_the_two_targets():
     handle = ctypes.CDLL(path)
     for name in ("e3j_b200_xla_convolution", "e3j_b200_xla_convolution_bwd"):
         assert hasattr(handle, name)
+
+
+@pytest.mark.skipif(not os.path.exists(_lib.XLA_LIB_PATH), reason="XLA FFI handler library not built")
+def test_e3j_ops_stand_in_module():
+    """`import e3j_ops` through the shim directory gives the three functions e3j's Python uses
+    (src/e3j/ops/__init__.py:15-24, src/e3j/ops/coef_ranges.py:36-51)."""
+    import importlib
+    import sys
+
+    shim = os.path.join(os.path.dirname(_lib.__file__), "shim")
+    sys.path.insert(0, shim)
+    try:
+        sys.modules.pop("e3j_ops", None)
+        mod = importlib.import_module("e3j_ops")
+    finally:
+        sys.path.remove(shim)
+    regs = mod.get_registrations()
+    assert sorted(regs) == ["convolution", "convolution_bwd"]
+    get_ptr = ctypes.pythonapi.PyCapsule_GetPointer
+    get_ptr.restype, get_ptr.argtypes = ctypes.c_void_p, (ctypes.py_object, ctypes.c_char_p)
+    handle = ctypes.CDLL(_lib.XLA_LIB_PATH)
+    for name, cap in regs.items():
+        want = ctypes.cast(getattr(handle, f"e3j_b200_xla_{name}"), ctypes.c_void_p).value
+        assert get_ptr(cap, b"xla._CUSTOM_CALL_TARGET") == want
+    assert mod.get_kernel_registers("convolution", "uint8", "float32", 4) > 0
+    with pytest.raises(ValueError):
+        mod.get_kernel_registers("tensor_product", "uint8", "float32", 4)
+    with pytest.raises(ValueError):
+        mod.get_kernel_registers("convolution", "int64", "float32", 4)

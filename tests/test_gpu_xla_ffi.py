@@ -89,3 +89,13 @@ def test_handler_errors_travel_as_xla_errors(xla):
                     torch.zeros(0, dtype=torch.int32, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV)],
                    [torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)], {"num_nodes": g.num_nodes, "debug": 0})  # fmt: skip
     assert len(errs) == 1 and "SENDER" in errs[0][1]
+
+
+def test_stand_in_module_device_properties():
+    """Keys of `e3j_ops.get_device_properties()` (lib/e3j_ops/ffi/e3j_ops.cpp:30-42)."""
+    from e3j_b200 import e3j_ops_compat
+
+    props = e3j_ops_compat.get_device_properties()
+    assert set(props) == {"device", "smem_max", "smem_opt_in", "smem_per_sm", "max_threads_per_sm",
+                          "max_blocks_per_sm", "regs_per_sm"}  # fmt: skip
+    assert props["smem_opt_in"] >= 200 * 1024 and props["regs_per_sm"] == 65536
