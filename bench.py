@@ -241,9 +241,12 @@ def run_ours(args):
         mark()
         ops.conv_fwd_raw(plan, x, y, s, graph, out)
         mark()
-        for ph in (1, 2, 4):
-            ops.conv_bwd_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds), phases=ph)
-            mark()
+        if events is None:
+            ops.conv_bwd_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds))
+        else:  # the three passes of the backward one by one, to time them
+            for ph in (1, 2, 4):
+                ops.conv_bwd_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds), phases=ph)
+                mark()
         if events is not None:
             events.append(marks)
 
@@ -267,10 +270,37 @@ def run_ours(args):
     barrier()
     events: list = []
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launch_mode = "eager"
+    cg = None
+    if not args.no_graph:
+        # The timed steps are replayed from a CUDA graph of one step, so that no host time sits between
+        # the step's launches (a step is 4-9 kernels of 7-340 us; issuing them from Python leaves gaps).
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                step()
+            cg.replay()
+            launch_mode = "cuda graph replay"
+        except Exception as exc:  # noqa: BLE001 - report and time the eager loop instead
+            print(f"bench: CUDA graph capture failed ({exc}); timing the eager loop", file=sys.stderr)
+            cg = None
+    barrier()
     t_start.record()
     for _ in range(args.steps):
-        step(events)
+        if cg is not None:
+            cg.replay()
+        else:
+            step()
     t_stop.record()
+    barrier()
+    # per-kernel times: the same steps issued one launch at a time with events in between
+    for _ in range(args.steps):
+        step(events)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms_total = t_start.elapsed_time(t_stop)
@@ -340,7 +370,7 @@ def run_ours(args):
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(cfg), "nodes_per_gpu": n, "edges_per_gpu": e_real, "channels": C,
-                   "variant": plan.variant, "parallelism": f"independent graphs x{world}",
+                   "variant": plan.variant, "parallelism": f"independent graphs x{world}", "launch": launch_mode,
                    "l2": "inputs larger than L2 (s and ds are %.0f MB each)" % (s.numel() * 4 / 1e6)},
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
@@ -678,6 +708,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="N = 1: issue the timed steps from Python instead of replaying a CUDA graph of one step")
     ap.add_argument("--window-edges", type=int, default=1 << 20, help="config 4: edges per window")
     ap.add_argument("--nodes", type=int, default=None, help="override the node count (small profiling cases)")
     args = ap.parse_args()
