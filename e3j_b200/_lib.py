@@ -132,6 +132,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_conv_fwd_rect.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, vp]
     lib.e3j_b200_conv_bwd_rect.restype = c.c_int
     lib.e3j_b200_conv_bwd_rect.argtypes = [vp] * 13 + [c.c_size_t, i32, i32, i64, i32, vp, i32]
+    lib.e3j_b200_conv_bwd_by_sender.restype = c.c_int
+    lib.e3j_b200_conv_bwd_by_sender.argtypes = [vp] * 13 + [c.c_size_t, i32, i32, i64, i32, vp]
     lib.e3j_b200_conv_fwd_window.restype = c.c_int
     lib.e3j_b200_conv_fwd_window.argtypes = [vp] * 7 + [i32, i32, i64, i64, i32, vp]
     lib.e3j_b200_conv_bwd_window.restype = c.c_int
@@ -172,6 +174,7 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_conv_bwd_static",
     "e3j_b200_conv_fwd_rect",
     "e3j_b200_conv_bwd_rect",
+    "e3j_b200_conv_bwd_by_sender",
     "e3j_b200_conv_fwd_window",
     "e3j_b200_conv_bwd_window",
     "e3j_b200_rows_gather",

@@ -46,9 +46,12 @@ class Convolution:
             source: representations of the node and edge features; the third
                 source space (one scalar per output irrep) is inferred.
             target: optional filter of multiplicity-1 irreps on the output.
-            graph_ordering: ``RECEIVER`` (edges sorted by receiver).  ``SENDER``
-                and ``NONE`` are accepted by the reference for other back ends
-                and raise ``NotImplementedError`` at call time here.
+            graph_ordering: ``RECEIVER`` (edges sorted by receiver) or ``SENDER``
+                (edges sorted by sender; as in the reference the forward then
+                aggregates over the reversed edges, which is the same sum for a
+                symmetric graph whose edge features flip with the edge direction,
+                src/e3j/core/convolution.py:236-246).  ``NONE`` raises
+                ``NotImplementedError`` at call time.
             layout: channel axis; only ``TRAILING_CHANNELS`` is supported by the
                 fused convolution (src/e3j/core/convolution.py:274-277).
             avg_num_neighbors: if given, folded into the coefficient values
@@ -95,7 +98,12 @@ class Convolution:
     def prepare_graph(self, num_nodes: int, senders: torch.Tensor, receivers: torch.Tensor) -> ConvGraph:
         """Derive the CSR views once for a graph that is reused across calls; pass
         the result as ``senders`` (``receivers`` is then ignored)."""
-        return ConvGraph.build(num_nodes, senders, receivers)
+        return ConvGraph.build(num_nodes, senders, receivers, self.graph_ordering)
+
+    @functools.cached_property
+    def y_parity(self) -> np.ndarray:
+        """O3 parity (+1 / -1) of every edge-feature component (src/e3j/core/convolution.py:238-246)."""
+        return np.concatenate([np.full(m * ir.dim, float(ir.p), dtype=np.float32) for m, ir in self._otimes.source[1]])
 
     def __call__(
         self,
@@ -112,8 +120,8 @@ class Convolution:
             node_features: (num_nodes, num_x, num_channels)
             edge_features: (num_edges, num_y)
             edge_scalars: (num_edges, num_scalars, num_channels)
-            senders, receivers: (num_edges,) indices, edges sorted by receiver;
-                ``DUMMY_INDEX`` marks padding edges.
+            senders, receivers: (num_edges,) indices, edges sorted by the endpoint
+                named by ``graph_ordering``; ``DUMMY_INDEX`` marks padding edges.
             node_mask: optional boolean (num_nodes,), ``False`` for trailing
                 padding nodes; edges touching them are dropped.
         """
@@ -135,6 +143,6 @@ class Convolution:
             receivers,
             self.params,
             self.graph_ordering,
-            None,
+            self.y_parity if self.graph_ordering == "SENDER" else None,
             force_generic=self.force_generic,
         )

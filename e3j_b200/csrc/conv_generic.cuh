@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_kernel(
 __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
     DeviceTable table, bool table_in_smem, const float *__restrict__ x, const float *__restrict__ y,
     const float *__restrict__ s, const float *__restrict__ dm, const int32_t *__restrict__ sender,
-    const int32_t *__restrict__ receiver_ptr, float *__restrict__ dxm, float *__restrict__ dy,
-    float *__restrict__ ds, int32_t N, int32_t NS, Dims d) {
+    const int32_t *__restrict__ receiver_ptr, const int32_t *__restrict__ edge_perm,
+    float *__restrict__ dxm, float *__restrict__ dy, float *__restrict__ ds, int32_t N, int32_t NS, Dims d) {
     extern __shared__ __align__(16) float smem_raw[];
     float *smem = smem_raw;
     const SmemTable tab = stage_table(table, table_in_smem, smem);
@@ -121,7 +121,10 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
          r += (int64_t)gridDim.x * blockDim.y) {
         const int32_t e0 = receiver_ptr[r], e1 = receiver_ptr[r + 1];
         const float *g = dm + (r * d.Z) * C;
-        for (int32_t e = e0; e < e1; e++) {
+        for (int32_t p = e0; p < e1; p++) {
+            // edge_perm: the per-edge arrays are stored in another order (sorted by sender);
+            // the p-th edge of the receiver-sorted list is row edge_perm[p] of them
+            const int32_t e = edge_perm ? edge_perm[p] : p;
             const int32_t a = sender[e];
             const bool valid = in_range(a, NS);
             for (int k = 0; k < d.Y; k++) dy_acc[k * CT + tx] = 0.f;
@@ -175,13 +178,32 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
 // receiver_ptr[N] belong to no receiver: their dy, ds and dx message are exact zeros
 // (lib/e3j_ops/cuda/convolution/bwd.cuh:308-319).
 // The buffers hold the edge window [e_begin, e_begin + E) of the CSR (e_begin = 0: all of it).
+// With `edge_perm` (per-edge arrays stored in another order, whole graph only) position p
+// of the receiver-sorted list is row edge_perm[p] of the buffers.
 __global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int32_t N, int64_t e_begin,
-                                  int64_t E, float *__restrict__ dxm, int64_t dxm_row,
+                                  int64_t E, const int32_t *__restrict__ edge_perm,
+                                  float *__restrict__ dxm, int64_t dxm_row,
                                   float *__restrict__ dy, int64_t dy_row, float *__restrict__ ds,
                                   int64_t ds_row, const float *__restrict__ dy_part, int nparts) {
     const int64_t first = max((int64_t)0, min((int64_t)receiver_ptr[N] - e_begin, E));
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (edge_perm) {
+        if (nparts > 1)
+            for (int64_t t = tid; t < first * dy_row; t += step) {
+                const int64_t at = (int64_t)edge_perm[t / dy_row] * dy_row + t % dy_row;
+                float v = dy_part[at];
+                for (int p = 1; p < nparts; p++) v += dy_part[(int64_t)p * E * dy_row + at];
+                dy[at] = v;
+            }
+        for (int64_t t = first * dxm_row + tid; t < E * dxm_row; t += step)
+            dxm[(int64_t)edge_perm[t / dxm_row] * dxm_row + t % dxm_row] = 0.f;
+        for (int64_t t = first * dy_row + tid; t < E * dy_row; t += step)
+            dy[(int64_t)edge_perm[t / dy_row] * dy_row + t % dy_row] = 0.f;
+        for (int64_t t = first * ds_row + tid; t < E * ds_row; t += step)
+            ds[(int64_t)edge_perm[t / ds_row] * ds_row + t % ds_row] = 0.f;
+        return;
+    }
     if (nparts > 1) {
         const int64_t total = first * dy_row, part = E * dy_row;
         if ((dy_row & 3) == 0) {  // rows of whole float4: 128-bit accesses
@@ -231,7 +253,7 @@ __global__ void __launch_bounds__(256) dx_reduce_kernel(const float *__restrict_
                 V t[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++)
-                    t[u] = reinterpret_cast<const V *>(dxm + (int64_t)perm_t[p + u] * XC)[v];
+                    t[u] = reinterpret_cast<const V *>(dxm + (int64_t)(perm_t ? perm_t[p + u] : p + u) * XC)[v];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const float *f = reinterpret_cast<const float *>(&t[u]);
@@ -240,7 +262,7 @@ __global__ void __launch_bounds__(256) dx_reduce_kernel(const float *__restrict_
                 }
             }
             for (; p < p1; p++) {
-                V t = reinterpret_cast<const V *>(dxm + (int64_t)perm_t[p] * XC)[v];
+                V t = reinterpret_cast<const V *>(dxm + (int64_t)(perm_t ? perm_t[p] : p) * XC)[v];
                 const float *f = reinterpret_cast<const float *>(&t);
 #pragma unroll
                 for (int q = 0; q < VEC; q++) acc[q] += f[q];

@@ -89,7 +89,7 @@ __global__ void untranspose_kernel(const int32_t *__restrict__ sender_ptr_t, con
     for (int64_t a = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; a < N;
          a += ((int64_t)gridDim.x * blockDim.x) >> 5) {
         for (int32_t p = sender_ptr_t[a] + lane; p < sender_ptr_t[a + 1]; p += 32) {
-            const int32_t e = perm_t[p];
+            const int32_t e = perm_t ? perm_t[p] : p;  // no permutation: the rows are stored in this order
             sender[e] = (int32_t)a;
             receiver[e] = recv_t[p];
         }

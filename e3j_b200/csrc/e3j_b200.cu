@@ -285,7 +285,7 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
                     const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
                     float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
                     int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases, int64_t e0,
-                    int window, int accumulate);
+                    int window, int accumulate, const int32_t *edge_perm = nullptr);
 
 int e3j_b200_conv_bwd_rect(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
                            const float *dm, const int32_t *sender, const int32_t *receiver_ptr,
@@ -308,6 +308,17 @@ int e3j_b200_conv_bwd_window(const e3j_b200_plan *p, const float *x, const float
                     accumulate != 0);
 }
 
+int e3j_b200_conv_bwd_by_sender(const e3j_b200_plan *p, const float *x, const float *y, const float *s,
+                                const float *dm, const int32_t *sender, const int32_t *sender_ptr,
+                                const int32_t *receiver_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                                float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                                int64_t E, int32_t debug, e3j_b200_stream stream) {
+    if (E > 0 && !perm_t) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    // per-edge pass grouped by receiver through perm_t; the dx sum runs over the stored (sender) order
+    return bwd_core(p, x, y, s, dm, sender, receiver_ptr_t, sender_ptr, nullptr, dx, dy, ds, workspace,
+                    workspace_bytes, N, NS, E, debug, stream, E3J_B200_BWD_ALL, 0, 0, 0, perm_t);
+}
+
 int e3j_b200_conv_fwd_window(const e3j_b200_plan *p, const float *x, const float *y_w, const float *s_w,
                              const int32_t *sender_w, const int32_t *receiver_ptr_w, float *out_w,
                              int32_t N, int32_t NS, int64_t e0, int64_t E, int32_t debug,
@@ -328,13 +339,14 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
                     const int32_t *sender_ptr_t, const int32_t *perm_t, float *dx, float *dy,
                     float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
                     int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases, int64_t e0,
-                    int window, int accumulate) {
+                    int window, int accumulate, const int32_t *edge_perm) {
     int rc = check_common(p, N, E);
+    if (edge_perm && window) return set_error(E3J_B200_UNIMPLEMENTED, "edge windows of sender-sorted edges");
     if (rc) return rc;
     if (NS < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative sender count");
     if (N == 0 && NS == 0) return E3J_B200_OK;
     if (!x || !dm || !dx || !receiver_ptr || !sender_ptr_t ||
-        (E > 0 && (!y || !s || !sender || !perm_t || !dy || !ds)))
+        (E > 0 && (!y || !s || !sender || (!perm_t && !edge_perm) || !dy || !ds)))
         return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
     if (workspace_bytes < e3j_b200_conv_bwd_workspace_bytes(p, N, E) || !workspace)
         return set_error(E3J_B200_INVALID_ARGUMENT, "workspace is too small");
@@ -355,7 +367,7 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
     if (E > 0 && (phases & E3J_B200_BWD_EDGES)) {
         if (p->variant != E3J_B200_VARIANT_GENERIC) {
             rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y0, s0, dm, sender0,
-                                            receiver_ptr, dxm0, dy_part0, ds0, N, NS, E, debug, stream);
+                                            receiver_ptr, edge_perm, dxm0, dy_part0, ds0, N, NS, E, debug, stream);
             if (rc) return rc;
         } else {
             const GenericGeometry g = generic_geometry(p);
@@ -372,14 +384,14 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
             const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
             DeviceTable t{p->d_val, p->d_idx, p->nnz};
             generic::conv_bwd_edges_kernel<<<grid, g.block, smem, stream>>>(
-                t, g.table_in_smem, x, y0, s0, dm, sender0, receiver_ptr, dxm0, dy0, ds0, N, NS, d);
+                t, g.table_in_smem, x, y0, s0, dm, sender0, receiver_ptr, edge_perm, dxm0, dy0, ds0, N, NS, d);
             rc = check_launch("convolution_bwd (edges)", debug, stream);
             if (rc) return rc;
         }
     }
     if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
         generic::bwd_finish_kernel<<<p->lim.sm_count * 8, 256, 0, stream>>>(
-            receiver_ptr, N, e0, E, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
+            receiver_ptr, N, e0, E, edge_perm, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
         rc = check_launch("convolution_bwd (tail)", debug, stream);
         if (rc) return rc;
     }
@@ -443,7 +455,7 @@ int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t 
 
 int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t, const int32_t *recv_t, int32_t N,
                              int64_t E, int32_t *sender, int32_t *receiver, e3j_b200_stream stream) {
-    if (N < 0 || E < 0 || !sender_ptr_t || (E > 0 && (!perm_t || !recv_t || !sender || !receiver)))
+    if (N < 0 || E < 0 || !sender_ptr_t || (E > 0 && (!recv_t || !sender || !receiver)))
         return set_error(E3J_B200_INVALID_ARGUMENT, "bad CSR operands");
     if (E == 0) return E3J_B200_OK;
     const int grid = (int)std::min<int64_t>(ceil_div64(E, 256), 148 * 8);

@@ -353,7 +353,7 @@ def emit_variant(em, v):
     em("struct Vals { float v[NNZ]; };")
     em(f"using DyAcc = {'float' if v.get('dyscalar') else 'float2'};  // per-lane accumulator of one dy component")
     em("struct FwdArgs { const float *x, *y, *s; const int32_t *sender, *receiver_ptr; float *out; int32_t N, NS; int64_t E; Vals vals; };")
-    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr; float *dxm, *dy, *ds; int32_t N, NS; int64_t E; Vals vals; };")
+    em("struct BwdArgs { const float *x, *y, *s, *dm; const int32_t *sender, *receiver_ptr, *edge_perm; float *dxm, *dy, *ds; int32_t N, NS; int64_t E; Vals vals; };")
     em()
     if v.get("fwd_groups"):
         groups = [sorted((paths[p] for p in g), key=lambda p: (p.lx, p.p)) for g in v["fwd_groups"]]

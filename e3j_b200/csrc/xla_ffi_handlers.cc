@@ -155,9 +155,6 @@ ffi::Error ConvolutionBwdImpl(cudaStream_t stream, ffi::ScratchAllocator scratch
     if (x.element_type() != ffi::F32 || dm.element_type() != ffi::F32)
         return ffi::Error(ffi::ErrorCode::kUnimplemented,
                           "E3J_ERROR[Unimplemented]: the B200 kernels compute in float32");
-    if (edge_perm.element_count() == 0 && y.dimensions()[0] != 0)
-        return ffi::Error(ffi::ErrorCode::kUnimplemented,
-                          "E3J_ERROR[Unimplemented]: SENDER graph ordering (empty edge_perm) is not supported");
     const auto dx = x.dimensions();
     const auto dy = y.dimensions();
     const int X = (int)dx[1], C = dx.size() > 2 ? (int)dx.back() : 1, Y = (int)dy[1];
@@ -187,6 +184,33 @@ ffi::Error ConvolutionBwdImpl(cudaStream_t stream, ffi::ScratchAllocator scratch
     auto round = [](size_t b) { return (b + 255) / 256 * 256; };
     const size_t idx_bytes = round((size_t)E * 4), ptr_bytes = round(((size_t)N + 2) * 4);
     const size_t ws_bytes = e3j_b200_conv_bwd_workspace_bytes(plan, N, E);
+    if (edge_perm.element_count() == 0 && E != 0) {
+        // SENDER graph ordering (src/e3j/ops/convolution.py:413-425): the edges are stored sorted by
+        // sender, `recv_t` holds their receivers and `sender_ptr_t` is the CSR of the stored order.
+        // The per-edge pass walks receivers, so build the receiver-sorted view of the stored edges.
+        const size_t tws_bytes = round(e3j_b200_csr_transpose_workspace_bytes(N, E));
+        auto mem = scratch.Allocate(3 * idx_bytes + ptr_bytes + tws_bytes + ws_bytes, 256);
+        if (!mem.has_value())
+            return ffi::Error(ffi::ErrorCode::kResourceExhausted, "E3J_ERROR[Internal]: scratch allocation failed");
+        char *base = static_cast<char *>(*mem);
+        int32_t *sender = reinterpret_cast<int32_t *>(base);
+        int32_t *receiver = reinterpret_cast<int32_t *>(base + idx_bytes);
+        int32_t *perm_r = reinterpret_cast<int32_t *>(base + 2 * idx_bytes);
+        int32_t *receiver_ptr = reinterpret_cast<int32_t *>(base + 3 * idx_bytes);
+        void *tws = base + 3 * idx_bytes + ptr_bytes;
+        void *workspace = base + 3 * idx_bytes + ptr_bytes + tws_bytes;
+        int rc = e3j_b200_csr_untranspose(sender_ptr_t.typed_data(), nullptr, recv_t.typed_data(), N, E, sender,
+                                          receiver, stream);
+        if (rc) return Status(rc);
+        rc = e3j_b200_csr_transpose(receiver, E, N, receiver_ptr, perm_r, tws, tws_bytes, stream);
+        if (rc) return Status(rc);
+        return Status(e3j_b200_conv_bwd_by_sender(plan, x.typed_data<float>(), y.typed_data<float>(),
+                                                  s.typed_data<float>(), dm.typed_data<float>(), sender,
+                                                  sender_ptr_t.typed_data(), receiver_ptr, perm_r,
+                                                  dxo->typed_data<float>(), dyo->typed_data<float>(),
+                                                  dso->typed_data<float>(), workspace, ws_bytes, N, N, E, debug,
+                                                  stream));
+    }
     auto mem = scratch.Allocate(2 * idx_bytes + ptr_bytes + ws_bytes, 256);
     if (!mem.has_value())
         return ffi::Error(ffi::ErrorCode::kResourceExhausted, "E3J_ERROR[Internal]: scratch allocation failed");

@@ -114,9 +114,19 @@ class ConvGraph:
     receiver_ptr: torch.Tensor  # int32 [N + 1]
     sender_ptr_t: torch.Tensor | None = None
     perm_t: torch.Tensor | None = None
+    #: "RECEIVER", or "SENDER" for an edge list stored sorted by sender.  The fields then hold
+    #: the swapped roles the reference's forward uses (src/e3j/ops/convolution.py:218-221):
+    #: `receiver` / `receiver_ptr` are the (sorted) true senders and their CSR offsets,
+    #: `sender` the true receivers, `transposed()` the receiver-sorted view of the stored edges.
+    ordering: str = "RECEIVER"
 
     @classmethod
-    def build(cls, num_nodes: int, sender: torch.Tensor, receiver: torch.Tensor) -> "ConvGraph":
+    def build(cls, num_nodes: int, sender: torch.Tensor, receiver: torch.Tensor,
+              ordering: str = "RECEIVER") -> "ConvGraph":  # fmt: skip
+        if ordering == "SENDER":
+            g = cls.build(num_nodes, receiver, sender)
+            g.ordering = "SENDER"
+            return g
         sender = sender.to(torch.int32).contiguous()
         receiver = receiver.to(torch.int32).contiguous()
         if receiver.device.type == "cuda":
@@ -221,15 +231,51 @@ def conv_bwd_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch
     return dx, dy, ds
 
 
+def conv_bwd_by_sender_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch.Tensor | None = None):
+    """Backward for a `SENDER`-ordered graph (``e3j_b200_conv_bwd_by_sender``): dy, ds in stored
+    order, dx summed over each sender's stored segment."""
+    if graph.ordering != "SENDER":
+        raise ValueError("conv_bwd_by_sender_raw needs a graph built with ordering='SENDER'")
+    dev = _require_cuda(x, y, s, dm, graph.sender, graph.receiver_ptr)
+    n, e = x.shape[0], int(y.shape[0])
+    receiver_ptr_t, perm_t = graph.transposed()  # over the true receivers (the `sender` field)
+    need = int(_lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, e))
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    dx, dy, ds = torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)
+    with torch.cuda.device(dev):
+        _lib.check(
+            _lib.lib().e3j_b200_conv_bwd_by_sender(
+                plan.handle, _ptr(x), _ptr(y), _ptr(s), _ptr(dm), _ptr(graph.receiver), _ptr(graph.receiver_ptr),
+                _ptr(receiver_ptr_t), _ptr(perm_t), _ptr(dx), _ptr(dy), _ptr(ds), _ptr(workspace),
+                workspace.numel() * workspace.element_size(), n, n, e, DEBUG_LEVEL, _stream(),
+            )
+        )  # fmt: skip
+    return dx, dy, ds
+
+
 # ---------------------------------------------------------------------------
 # differentiable primitives
 # ---------------------------------------------------------------------------
+# `plan` is the plan of the forward table; under SENDER ordering it is a pair
+# (forward plan with the y parities folded into the values, backward plan without them).
+def _fwd_plan(plan):
+    return plan[0] if isinstance(plan, tuple) else plan
+
+
+def _bwd_raw(plan, x, y, s, dm, graph):
+    if graph.ordering == "SENDER":
+        return conv_bwd_by_sender_raw(plan[1], x, y, s, dm, graph)
+    return conv_bwd_raw(plan, x, y, s, dm, graph)
+
+
+
 class _ConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, y, s, plan, graph):
         ctx.plan, ctx.graph = plan, graph
         ctx.save_for_backward(x, y, s)
-        return conv_fwd_raw(plan, x, y, s, graph)
+        return conv_fwd_raw(_fwd_plan(plan), x, y, s, graph)
 
     @staticmethod
     def backward(ctx, dm):
@@ -243,7 +289,7 @@ class _ConvBwdFn(torch.autograd.Function):
     def forward(ctx, x, y, s, dm, plan, graph):
         ctx.plan, ctx.graph = plan, graph
         ctx.save_for_backward(x, y, s, dm)
-        return conv_bwd_raw(plan, x, y, s, dm, graph)
+        return _bwd_raw(plan, x, y, s, dm, graph)
 
     @staticmethod
     def backward(ctx, ddx, ddy, dds):
@@ -285,13 +331,15 @@ def _check_operands(coef, x, y, s):
             )
 
 
-def _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic=False):
+def _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic=False, y_parity=None):
     _check_operands(coef, x, y, s)
     ordering = str(graph_ordering).upper().split(".")[-1]
     if ordering not in GRAPH_ORDERINGS:
         raise ValueError(f"unknown graph ordering {graph_ordering!r}")
-    if ordering != "RECEIVER":
-        raise NotImplementedError("the B200 convolution supports RECEIVER graph ordering only.")
+    if ordering == "NONE":
+        raise NotImplementedError("CUDA convolution only supports SENDER and RECEIVER ordering.")
+    if ordering == "SENDER" and y_parity is None:
+        raise ValueError("SENDER graph ordering requires `y_parity`.")
     if y.ndim == 3:
         y = y[..., 0]
     dev = _require_cuda(x, y, s)
@@ -299,11 +347,21 @@ def _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_gene
     if s.shape[1] != dims[3] or s.shape[2] != dims[4] or s.shape[0] != y.shape[0]:
         raise ValueError(f"edge scalars of shape {tuple(s.shape)} do not match (E, {dims[3]}, {dims[4]})")
     plan = get_plan(np.asarray(coef), dims, dev, force_generic)
+    if ordering == "SENDER":
+        # forward over the reversed edges: the y parities sign the forward values only
+        # (src/e3j/ops/convolution.py:166-176)
+        c = Coef4D.unpack(np.asarray(coef), np.float32)
+        signs = np.asarray(y_parity, dtype=c.val.dtype)[c.idx[:, 2]]
+        signed = Coef4D(c.val * signs, c.idx, val_dtype=c.val_dtype, idx_dtype=c.idx_dtype).pack()
+        plan = (get_plan(signed, dims, dev, force_generic), plan)
     if isinstance(sender, ConvGraph):
         graph = sender
+        if graph.ordering != ordering:
+            raise ValueError(f"the prepared graph is {graph.ordering}-ordered, the operator {ordering}-ordered")
     else:
         n = int(x.shape[0])
-        graph = ConvGraph.build(n, _wrap_global_index(sender.to(dev), n), _wrap_global_index(receiver.to(dev), n))
+        graph = ConvGraph.build(n, _wrap_global_index(sender.to(dev), n), _wrap_global_index(receiver.to(dev), n),
+                                ordering)  # fmt: skip
     return plan, graph, x.contiguous(), y.contiguous(), s.contiguous()
 
 
@@ -317,8 +375,7 @@ def convolution(coef, x, y, s, sender, receiver, params, graph_ordering="RECEIVE
     may also be a prepared :class:`ConvGraph`), ``params`` with ``num_out`` and
     ``num_scalars``.  Returns (N, Z, C).
     """
-    del y_parity  # only read under SENDER ordering
-    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic)
+    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic, y_parity)
     return _ConvFn.apply(x, y, s, plan, graph)
 
 
@@ -326,8 +383,7 @@ def convolution_bwd(coef, x, y, s, sender, receiver, dm, params, graph_ordering=
                     *, force_generic: bool = False):  # fmt: skip
     """Cotangents ``(dx, dy, ds)`` for the output cotangent ``dm``; ``coef`` is the
     *forward* table, as in src/e3j/ops/convolution.py:334-365."""
-    del y_parity
-    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic)
+    plan, graph, x, y, s = _prepare(coef, x, y, s, sender, receiver, params, graph_ordering, force_generic, y_parity)
     return _ConvBwdFn.apply(x, y, s, dm.contiguous(), plan, graph)
 
 

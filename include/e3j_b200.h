@@ -166,6 +166,25 @@ int e3j_b200_conv_bwd_rect(const e3j_b200_plan *plan, const float *x, const floa
                            int64_t E, int32_t debug, e3j_b200_stream stream, int32_t phases);
 
 /*
+ * Backward for edges stored sorted by SENDER (the reference's SENDER graph ordering: the
+ * direct CSR groups by sender and no edge permutation is passed,
+ * src/e3j/ops/convolution.py:413-425).  x, y, s, dm are as in e3j_b200_conv_bwd_rect;
+ *   sender[E]          stored order (ascending; padding = out of range, at the tail),
+ *   sender_ptr[NS + 1] CSR offsets of `sender`,
+ *   receiver_ptr_t[N + 1], perm_t[E]  the receiver-sorted view of the same edges:
+ *                      position p of the receiver-major list is stored edge perm_t[p]
+ *                      (what e3j_b200_csr_transpose returns for the receiver array).
+ * dy, ds are written in stored order; dx[a] sums the messages of the stored segment of a.
+ * The per-edge pass still walks receivers (dm[r] staged once per receiver); only the rows
+ * of the per-edge arrays are reached through perm_t.
+ */
+int e3j_b200_conv_bwd_by_sender(const e3j_b200_plan *plan, const float *x, const float *y, const float *s,
+                                const float *dm, const int32_t *sender, const int32_t *sender_ptr,
+                                const int32_t *receiver_ptr_t, const int32_t *perm_t, float *dx, float *dy,
+                                float *ds, void *workspace, size_t workspace_bytes, int32_t N, int32_t NS,
+                                int64_t E, int32_t debug, e3j_b200_stream stream);
+
+/*
  * Edge windows (no counterpart in the reference): a graph whose per-edge operands do
  * not fit in memory at once is run as consecutive receiver ranges, the per-edge scalars
  * of each range being produced just before use.  A window is the receivers
@@ -224,6 +243,8 @@ int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t 
  * kernel (lib/e3j_ops/ffi/e3j_ops.h:478-494: the sender CSR `sender_ptr_t`, the per-edge
  * receivers in sender order `recv_t`, and `perm_t`): writes the receiver-sorted
  * sender[E] and receiver[E]; edges found in no sender row get the padding index INT32_MAX.
+ * `perm_t` may be null (the edges are stored in sender order, the reference's SENDER graph
+ * ordering): the outputs are then the per-edge senders and receivers in that stored order.
  */
 int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t, const int32_t *recv_t, int32_t N,
                              int64_t E, int32_t *sender, int32_t *receiver, e3j_b200_stream stream);

@@ -81,14 +81,29 @@ def test_handler_errors_travel_as_xla_errors(xla):
     errs = rt.call(xla.e3j_b200_xla_convolution, [coef_dev, x.double(), y, s, graph.sender, graph.receiver_ptr.contiguous(), ranges],
                    [out], {"num_nodes": g.num_nodes, "debug": 0})  # fmt: skip
     assert len(errs) == 1 and "float32" in errs[0][1]
-    # SENDER ordering reaches the backward as an empty edge_perm
-    dm = torch.randn_like(out)
+
+
+def test_backward_handler_under_sender_ordering(xla):
+    """SENDER ordering reaches the backward as an empty edge_perm, the receivers of the stored
+    (sender-sorted) edges and the CSR of the stored order (src/e3j/ops/convolution.py:413-425)."""
+    conv, g, c, x, y, s, snd, rcv = _case(0, 200, "uint8")
+    n, z = g.num_nodes, conv.target.dim
+    order = torch.as_tensor(np.lexsort((g.receiver, g.sender))).to(DEV)
+    snd_s, rcv_s, y_s, s_s = snd[order].contiguous(), rcv[order].contiguous(), y[order].contiguous(), s[order].contiguous()
+    plan = ops.get_plan(conv._coef_packed, (x.shape[1], 16, z, conv.num_scalars, 128), DEV)
+    graph = ops.ConvGraph.build(n, snd_s, rcv_s, "SENDER")
+    dm = torch.randn((n, z, 128), device=DEV)
+    wdx, wdy, wds = ops.conv_bwd_by_sender_raw(plan, x, y_s, s_s, dm, graph)
+    rt = FakeRuntime(DEV)
     coef3 = np.stack([c.transpose(a).pack() for a in ((1, 0, 2, 3), (2, 0, 1, 3), (3, 0, 2, 1))])
+    dx, dy, ds = (torch.full_like(t, float("nan")) for t in (x, y_s, s_s))
     errs = rt.call(xla.e3j_b200_xla_convolution_bwd,
-                   [torch.as_tensor(coef3).to(DEV), x, y, s, dm, graph.sender, graph.receiver_ptr.contiguous(),
+                   [torch.as_tensor(coef3).to(DEV), x, y_s, s_s, dm, rcv_s, graph.receiver_ptr.contiguous(),
                     torch.zeros(0, dtype=torch.int32, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV)],
-                   [torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)], {"num_nodes": g.num_nodes, "debug": 0})  # fmt: skip
-    assert len(errs) == 1 and "SENDER" in errs[0][1]
+                   [dx, dy, ds], {"num_nodes": n, "debug": 1})  # fmt: skip
+    assert errs == []
+    torch.cuda.synchronize()
+    assert torch.equal(dx, wdx) and torch.equal(dy, wdy) and torch.equal(ds, wds)
 
 
 def test_stand_in_module_device_properties():
