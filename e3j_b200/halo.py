@@ -7,9 +7,10 @@ graph is split into spatial slabs (`e3j_b200.partition`); every step
   forward   pack the owned rows the neighbours need -> post sends / receives of halo
             x rows -> convolve the *interior* receivers (all senders owned) while the
             halo is in flight -> wait -> convolve the boundary receivers;
-  backward  per-edge pass over the owned receivers -> sum the dx messages per local
-            sender (owned and halo) -> return the halo rows' partial dx to their owners
-            -> owners add them in ascending peer order.
+  backward  per-edge pass over the owned receivers -> sum the dx messages of the halo
+            senders -> post their return to the owners -> sum the dx messages of the owned
+            senders while those rows travel -> owners add the returned rows in ascending
+            peer order.
 
 Point-to-point transfers only (each rank talks to the slabs next to it); payloads land
 in this GPU's own memory before any kernel reads them.  The row packing / adding and
@@ -62,15 +63,34 @@ class CudaConvOps:
             vp(receiver_ptr.data_ptr() + 4 * r0), vp(out.data_ptr() + 4 * r0 * z * c), r1 - r0, n_send,
             int(y.shape[0]), ops.DEBUG_LEVEL, ops._stream()))  # fmt: skip
 
-    def backward(self, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, n_recv, n_send) -> None:
+    #: the dx reduction can be run on a range of sender rows (`backward(..., rows=...)`), which lets the
+    #: partitioned operator send the halo rows of dx while the owned rows are still being summed
+    split_dx = True
+
+    def backward(self, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, n_recv, n_send,
+                 phases: int = 7, rows: tuple[int, int] | None = None) -> None:
+        """`phases` as in e3j_b200_conv_bwd_phases (1 per-edge pass, 2 finish, 4 dx reduction);
+        `rows` = (a0, a1) restricts the dx reduction to those sender rows."""
         e = int(y.shape[0])
         need = int(_lib.lib().e3j_b200_conv_bwd_workspace_bytes(self.plan.handle, n_recv, e))
         if self.workspace is None or self.workspace.numel() < need:
             self.workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        vp = ctypes.c_void_p
+        ptr_t, dx_p, ns = ops._ptr(sender_ptr_t), ops._ptr(dx), n_send
+        if rows is not None:
+            if phases != 4:
+                raise ValueError("a row range applies to the dx reduction alone (phases = 4)")
+            a0, a1 = rows
+            if a1 <= a0:
+                return
+            ptr_t = vp(sender_ptr_t.data_ptr() + 4 * a0)
+            dx_p = vp(dx.data_ptr() + 4 * a0 * dx[0].numel())
+            ns = a1 - a0
         _lib.check(_lib.lib().e3j_b200_conv_bwd_rect(
             self.plan.handle, ops._ptr(x), ops._ptr(y), ops._ptr(s), ops._ptr(dm), ops._ptr(sender),
-            ops._ptr(receiver_ptr), ops._ptr(sender_ptr_t), ops._ptr(perm_t), ops._ptr(dx), ops._ptr(dy), ops._ptr(ds),
-            ops._ptr(self.workspace), self.workspace.numel(), n_recv, n_send, e, ops.DEBUG_LEVEL, ops._stream(), 7))  # fmt: skip
+            ops._ptr(receiver_ptr), ptr_t, ops._ptr(perm_t), dx_p, ops._ptr(dy), ops._ptr(ds),
+            ops._ptr(self.workspace), self.workspace.numel(), n_recv, ns, e, ops.DEBUG_LEVEL, ops._stream(),
+            int(phases)))  # fmt: skip
 
 
 @dataclass
@@ -129,19 +149,27 @@ class HaloConvolution:
                 recvs.append((p.rank, x_loc[p.recv[0] : p.recv[1]]))
         return self._post(sends, recvs)
 
-    def reverse_exchange(self, dx_loc: torch.Tensor) -> None:
-        """Return the halo rows of dx to their owners and add what the peers return."""
+    def start_reverse_exchange(self, dx_loc: torch.Tensor):
+        """Post the return of the halo rows of dx to their owners and the receives of what the
+        peers return."""
         sends, recvs = [], []
         for p in self.peers:
             if p.recv is not None and p.recv[1] > p.recv[0]:
                 sends.append((p.rank, dx_loc[p.recv[0] : p.recv[1]]))
             if p.send_rows is not None and p.send_rows.numel():
                 recvs.append((p.rank, self._recv_dx[p.rank]))
-        for w in self._post(sends, recvs):
+        return self._post(sends, recvs)
+
+    def finish_reverse_exchange(self, works, dx_loc: torch.Tensor) -> None:
+        for w in works:
             w.wait()
         for p in self.peers:  # ascending peer order: fixed summation order
             if p.send_rows is not None and p.send_rows.numel():
                 self.rows.add(dx_loc, p.send_rows, self._recv_dx[p.rank])
+
+    def reverse_exchange(self, dx_loc: torch.Tensor) -> None:
+        """Return the halo rows of dx to their owners and add what the peers return."""
+        self.finish_reverse_exchange(self.start_reverse_exchange(dx_loc), dx_loc)
 
     # -- operator -------------------------------------------------------------
     def forward(self, x_loc: torch.Tensor, y: torch.Tensor, s: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -159,7 +187,16 @@ class HaloConvolution:
         """Cotangents for `dm` (n_own, Z, C): `dx_loc` (n_loc rows; on return the owned rows
         hold the full dx, including what other ranks' edges contributed), `dy`, `ds`."""
         part = self.part
-        self.conv.backward(x_loc, y, s, dm, self.sender, self.receiver_ptr, self.sender_ptr_t, self.perm_t,
-                           dx_loc, dy, ds, part.n_own, part.n_loc)  # fmt: skip
-        self.reverse_exchange(dx_loc)
+        args = (x_loc, y, s, dm, self.sender, self.receiver_ptr, self.sender_ptr_t, self.perm_t, dx_loc, dy, ds,
+                part.n_own, part.n_loc)  # fmt: skip
+        if getattr(self.conv, "split_dx", False) and self.peers:
+            # halo rows of dx first, so that they travel while the owned rows are summed
+            self.conv.backward(*args, phases=3)
+            self.conv.backward(*args, phases=4, rows=(part.n_own, part.n_loc))
+            works = self.start_reverse_exchange(dx_loc)
+            self.conv.backward(*args, phases=4, rows=(0, part.n_own))
+            self.finish_reverse_exchange(works, dx_loc)
+        else:
+            self.conv.backward(*args)
+            self.reverse_exchange(dx_loc)
         return dx_loc, dy, ds

@@ -207,3 +207,34 @@ def test_cuda_path_with_ranks_emulated_on_one_gpu(world):
                 CudaRowOps.add(dx_locs[p.rank], peer.send_rows, dx_locs[peer.rank][a:b].contiguous())
     for p, h, _ in ranks:
         assert_close(dx_locs[p.rank][: p.n_own].cpu().numpy(), dx_g[p.global_ids[: p.n_own]], what=f"dx rank {p.rank}")
+
+
+@pytest.mark.gpu
+def test_dx_reduction_by_row_ranges_equals_one_call():
+    """The partitioned backward sums the halo rows of dx first (they travel while the owned rows
+    are summed): per-edge pass, then the dx reduction on two row ranges = one full call, bitwise."""
+    from e3j_b200 import ops
+    from e3j_b200.halo import CudaConvOps, CudaRowOps, HaloConvolution
+
+    dev = torch.device("cuda:0")
+    g, conv, x, y, s, dm, parts = _global_case(2, nodes_per_slab=300)
+    dims = (4, 16, conv.target.dim, conv.num_scalars, 128)
+    plan = ops.get_plan(conv._coef_packed, dims, dev)
+    p = parts[0]
+    h = HaloConvolution(p, dims, dev, CudaConvOps(plan), CudaRowOps)
+    x_loc = torch.from_numpy(x[p.global_ids]).to(dev)
+    y_l, s_l = torch.from_numpy(y[p.edge_ids]).to(dev), torch.from_numpy(s[p.edge_ids]).to(dev)
+    dm_l = torch.from_numpy(dm[p.global_ids[: p.n_own]]).to(dev)
+    args = lambda dx, dy, ds: (x_loc, y_l, s_l, dm_l, h.sender, h.receiver_ptr, h.sender_ptr_t, h.perm_t, dx, dy, ds,
+                               p.n_own, p.n_loc)  # noqa: E731
+    one = [torch.full_like(t, float("nan")) for t in (x_loc, y_l, s_l)]
+    h.conv.backward(*args(*one))
+    two = [torch.full_like(t, float("nan")) for t in (x_loc, y_l, s_l)]
+    h.conv.backward(*args(*two), phases=3)
+    h.conv.backward(*args(*two), phases=4, rows=(p.n_own, p.n_loc))
+    assert not torch.isnan(two[0][p.n_own :]).any() and torch.isnan(two[0][: p.n_own]).all()
+    h.conv.backward(*args(*two), phases=4, rows=(0, p.n_own))
+    for a, b in zip(one, two):
+        assert torch.equal(a, b)
+    with pytest.raises(ValueError):
+        h.conv.backward(*args(*two), phases=7, rows=(0, 1))
