@@ -167,7 +167,7 @@ def emit_y_loads(em, ks):
 # ---------------------------------------------------------------------------
 # forward
 # ---------------------------------------------------------------------------
-def emit_fwd_group(em, vname, gi, group, dims):
+def emit_fwd_group(em, vname, gi, group, dims, uform=False):
     X, Y, Z, S = dims
     srows = [p.p for p in group]
     xrows = sorted({j for p in group for j in p.xrows})
@@ -211,6 +211,17 @@ def emit_fwd_group(em, vname, gi, group, dims):
                 em(f"const f4 x{j} = ld4(sg + {slot_x[j]} * 32);")
         em.block("")
         em(f"const f4 sv = ld4(sg + {slot_s[path.p]} * 32);  // path {path.p}")
+        if uform and len(path.zs) > len(path.js):
+            # more output rows than x rows: scale the x rows by s once, then accumulate straight
+            # into the output rows (len(js) products instead of len(zs))
+            for j in path.js:
+                em(f"const f4 u{j} = mul_vv(sv, x{j});")
+            for z in path.zs:
+                for (zz, j) in path.pairs:
+                    if zz == z:
+                        em(f"fma_sv(c.a{z}, {weight_expr(path, z, j)[0]}, u{j});")
+            em.end()
+            continue
         for z in path.zs:
             js = [j for (zz, j) in path.pairs if zz == z]
             em(f"{{ f4 t = mul_sv({weight_expr(path, z, js[0])[0]}, x{js[0]});")
@@ -360,7 +371,7 @@ def emit_variant(em, v):
         assert sorted(p.p for g in groups for p in g) == list(range(S)) and len(groups) == nw
     else:
         groups = group_paths(paths, nw)
-    rows = [emit_fwd_group(em, name, gi, g, (X, Y, Z, S)) for gi, g in enumerate(groups)]
+    rows = [emit_fwd_group(em, name, gi, g, (X, Y, Z, S), bool(v.get("uform"))) for gi, g in enumerate(groups)]
     em(f"static constexpr int kFwdMaxRows = {max(rows)};")
     chunks = emit_bwd(em, name, paths, (X, Y, Z, S), v["slot_rows"])
     em("#include \"conv_unrolled_kernels.inc\"")
