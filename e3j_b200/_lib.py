@@ -148,6 +148,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_csr_transpose_workspace_bytes.argtypes = [i32, i64]
     lib.e3j_b200_csr_transpose.restype = c.c_int
     lib.e3j_b200_csr_transpose.argtypes = [vp, i64, i32, vp, vp, vp, c.c_size_t, vp]
+    lib.e3j_b200_check_graph.restype = c.c_int
+    lib.e3j_b200_check_graph.argtypes = [vp, vp, i32, i32, i64, c.POINTER(c.c_int32), vp]
     lib.e3j_b200_csr_untranspose.restype = c.c_int
     lib.e3j_b200_csr_untranspose.argtypes = [vp, vp, vp, i32, i64, vp, vp, vp]
     lib.e3j_b200_harmonics_fwd.restype = c.c_int
@@ -183,6 +185,7 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_csr_transpose_workspace_bytes",
     "e3j_b200_csr_transpose",
     "e3j_b200_csr_untranspose",
+    "e3j_b200_check_graph",
     "e3j_b200_harmonics_fwd",
     "e3j_b200_harmonics_bwd",
 )

@@ -96,6 +96,36 @@ __global__ void untranspose_kernel(const int32_t *__restrict__ sender_ptr_t, con
     }
 }
 
+// Consistency of the CSR view the convolution kernels are given, counted into report[0..3]:
+// [0] offsets that decrease (receiver_ptr[r] > receiver_ptr[r + 1]) or lie outside [0, E],
+// [1] edges inside a segment whose sender is outside [0, NS) (skipped by the kernels: padding),
+// [2] edges at or beyond receiver_ptr[N] (belong to no receiver: their cotangents are zeros),
+// [3] edges inside a segment whose sender is negative or in [NS, INT32_MAX): not the padding
+//     sentinel, most likely a wrong index.
+__global__ void check_graph_kernel(const int32_t *__restrict__ sender, const int32_t *__restrict__ receiver_ptr,
+                                   int32_t N, int32_t NS, int64_t E, int32_t *__restrict__ report) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+    int bad_ptr = 0, skipped = 0, stray = 0;
+    for (int64_t r = tid; r <= N; r += step) {
+        const int64_t a = receiver_ptr[r];
+        if (a < 0 || a > E) bad_ptr++;
+        else if (r < N && a > receiver_ptr[r + 1]) bad_ptr++;
+    }
+    const int64_t last = receiver_ptr[N];
+    const int64_t covered = last < 0 ? 0 : (last > E ? E : last);
+    for (int64_t e = tid; e < covered; e += step) {
+        const int32_t a = sender[e];
+        if (!in_range(a, NS)) {
+            skipped++;
+            if (a != 0x7fffffff) stray++;
+        }
+    }
+    if (bad_ptr) atomicAdd(&report[0], bad_ptr);
+    if (skipped) atomicAdd(&report[1], skipped);
+    if (stray) atomicAdd(&report[3], stray);
+    if (tid == 0) report[2] = (int32_t)min((int64_t)0x7fffffff, E - covered);
+}
+
 __global__ void fill_i32_kernel(int32_t *__restrict__ dst, int64_t n, int32_t value) {
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
         dst[t] = value;

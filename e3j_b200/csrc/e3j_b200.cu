@@ -467,6 +467,32 @@ int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t,
     return check_launch("csr_untranspose", 0, stream);
 }
 
+int e3j_b200_check_graph(const int32_t *sender, const int32_t *receiver_ptr, int32_t N, int32_t NS, int64_t E,
+                         int32_t *report_host, e3j_b200_stream stream) {
+    if (N < 0 || NS < 0 || E < 0 || !receiver_ptr || !report_host || (E > 0 && !sender))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "bad graph operands");
+    int32_t *report = nullptr;
+    E3JB_CUDA_TRY(cudaMalloc(&report, 4 * sizeof(int32_t)));
+    cudaError_t err = cudaMemsetAsync(report, 0, 4 * sizeof(int32_t), stream);
+    if (err == cudaSuccess) {
+        const int grid = (int)std::min<int64_t>(ceil_div64(std::max<int64_t>(E, (int64_t)N + 1), 256), 148 * 8);
+        csr::check_graph_kernel<<<grid, 256, 0, stream>>>(sender, receiver_ptr, N, NS, E, report);
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess)
+        err = cudaMemcpyAsync(report_host, report, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    cudaFree(report);
+    if (err != cudaSuccess) return set_error(E3J_B200_CUDA_RUNTIME, cudaGetErrorString(err));
+    if (report_host[0] > 0) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "receiver_ptr is not a CSR offset array of %lld edges (%d bad entries)",
+                 (long long)E, report_host[0]);
+        return set_error(E3J_B200_INVALID_ARGUMENT, msg);
+    }
+    return E3J_B200_OK;
+}
+
 // ---------------------------------------------------------------------------
 // harmonics of edge vectors
 // ---------------------------------------------------------------------------

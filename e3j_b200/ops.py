@@ -157,6 +157,22 @@ class ConvGraph:
         return self.sender_ptr_t, self.perm_t
 
 
+def check_graph(graph: ConvGraph, num_edges: int | None = None, num_senders: int | None = None) -> dict:
+    """Validate a graph on its device before the kernels trust it (synchronises).  Raises
+    :class:`e3j_b200._lib.E3JError` when `receiver_ptr` is not a CSR offset array; otherwise
+    returns counts of edges the kernels will skip: ``padding`` (sender out of range inside a
+    segment), ``unassigned`` (beyond the last segment) and ``suspicious`` (out-of-range senders
+    that are not the padding index)."""
+    dev = _require_cuda(graph.sender, graph.receiver_ptr)
+    e = int(graph.sender.numel()) if num_edges is None else int(num_edges)
+    ns = graph.num_nodes if num_senders is None else int(num_senders)
+    report = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().e3j_b200_check_graph(_ptr(graph.sender), _ptr(graph.receiver_ptr),
+                                                   graph.receiver_ptr.numel() - 1, ns, e, report, _stream()))  # fmt: skip
+    return {"padding": int(report[1]), "unassigned": int(report[2]), "suspicious": int(report[3])}
+
+
 def _wrap_global_index(index: torch.Tensor, num_nodes: int) -> torch.Tensor:
     """Reduce indices modulo ``num_nodes`` keeping the padding sentinel out of
     range (src/e3j/ops/convolution.py:39-51)."""

@@ -239,6 +239,20 @@ size_t e3j_b200_csr_transpose_workspace_bytes(int32_t N, int64_t E);
 int e3j_b200_csr_transpose(const int32_t *sender, int64_t E, int32_t N, int32_t *sender_ptr_t, int32_t *perm_t,
                            void *workspace, size_t workspace_bytes, e3j_b200_stream stream);
 /*
+ * Checks the graph operands of the convolution calls before they are trusted (no counterpart
+ * in the reference, which reads them unchecked): synchronises the stream and fills
+ * report[4] (host memory) with the number of
+ *   [0] entries of receiver_ptr that decrease or lie outside [0, E]  -> the call fails with
+ *       E3J_B200_INVALID_ARGUMENT: the kernels would read out of bounds,
+ *   [1] edges inside a segment whose sender is outside [0, NS) (skipped as padding),
+ *   [2] edges at or beyond receiver_ptr[N] (no receiver; zero cotangents),
+ *   [3] of the edges in [1], those whose sender is not the padding index INT32_MAX.
+ * Only the two index arrays are read, always in bounds.
+ */
+int e3j_b200_check_graph(const int32_t *sender, const int32_t *receiver_ptr, int32_t N, int32_t NS, int64_t E,
+                         int32_t *report_host, e3j_b200_stream stream);
+
+/*
  * Inverse view, for a caller that only holds what the reference hands its backward
  * kernel (lib/e3j_ops/ffi/e3j_ops.h:478-494: the sender CSR `sender_ptr_t`, the per-edge
  * receivers in sender order `recv_t`, and `perm_t`): writes the receiver-sorted

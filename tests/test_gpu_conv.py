@@ -326,3 +326,27 @@ def test_device_csr_matches_stable_argsort(n, e, pad):
     assert perm_t.cpu().tolist() == perm_ref.tolist()  # padding edges last, in order
     again = ops.ConvGraph.build(n, dev(snd), dev(rcv)).transposed()[1]
     assert torch.equal(again, perm_t)
+
+
+def test_check_graph_reports_and_rejects():
+    """The validation pass (reads the two index arrays only): counts of padding / unassigned /
+    suspicious edges, and an error for offsets that are not a CSR array."""
+    from e3j_b200 import _lib
+
+    rng = np.random.default_rng(3)
+    n, e, pad = 50, 600, 9
+    snd, rcv = random_graph(rng, n, e - pad)
+    snd[5] = problems.DUMMY_INDEX  # a padding edge inside a segment
+    snd[17] = -3  # out of range, but not the padding index
+    snd = np.concatenate([snd, [problems.DUMMY_INDEX] * pad]).astype(np.int32)
+    rcv = np.concatenate([rcv, [problems.DUMMY_INDEX] * pad]).astype(np.int32)
+    graph = ops.ConvGraph.build(n, dev(snd), dev(rcv))
+    assert ops.check_graph(graph) == {"padding": 2, "unassigned": pad, "suspicious": 1}
+    ptr = graph.receiver_ptr.clone()
+    ptr[10], ptr[30] = graph.receiver_ptr[30], graph.receiver_ptr[10]
+    bad = ops.ConvGraph(n, graph.sender, graph.receiver, ptr)
+    with pytest.raises(_lib.E3JError, match="InvalidArgument"):
+        ops.check_graph(bad)
+    too_long = ops.ConvGraph(n, graph.sender[:100].contiguous(), graph.receiver, graph.receiver_ptr)
+    with pytest.raises(_lib.E3JError, match="InvalidArgument"):
+        ops.check_graph(too_long)  # offsets beyond the 100 edges given
