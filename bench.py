@@ -210,13 +210,32 @@ def run_ours(args):
         return run_ours_config4(args, world, rank, local, device)
 
     cfg = args.config
-    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER",
+    by_sender = args.ordering == "SENDER"
+    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering=args.ordering,
                        avg_num_neighbors=30.0)  # fmt: skip
     g = problems.make_graph(cfg, seed=rank, num_nodes=args.nodes)
     x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
     X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
     plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
-    graph = conv.prepare_graph(g.num_nodes, torch.as_tensor(g.sender).to(device), torch.as_tensor(g.receiver).to(device))
+    snd_h, rcv_h = g.sender, g.receiver
+    if by_sender:
+        # the same edges stored sorted by sender (padding stays last); the forward then runs over the
+        # reversed edges with the y parities folded into the table, as the reference does
+        order = np.lexsort((rcv_h, snd_h))
+        snd_h, rcv_h = snd_h[order], rcv_h[order]
+        order_d = torch.as_tensor(order).to(device)
+        y = y[order_d].contiguous()
+        s_sorted = torch.empty_like(s)
+        torch.index_select(s, 0, order_d, out=s_sorted)
+        s = s_sorted
+        del s_sorted
+        from e3j_b200.coef import Coef4D
+
+        signed = Coef4D(conv.coef.val * conv.y_parity[conv.coef.idx[:, 2]], conv.coef.idx, idx_dtype=conv.coef.idx_dtype)
+        plan_fwd = ops.get_plan(signed.pack(), (X, Y, Z, S, C), device)
+    else:
+        plan_fwd = plan
+    graph = conv.prepare_graph(g.num_nodes, torch.as_tensor(snd_h).to(device), torch.as_tensor(rcv_h).to(device))
     graph.transposed()
     n, e, e_real = g.num_nodes, int(g.sender.shape[0]), int(g.num_real_edges)
 
@@ -224,10 +243,11 @@ def run_ours(args):
     dx, dy, ds = torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)
     need = int(ops._lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, e))
     ws = torch.empty(need, dtype=torch.uint8, device=device)
-    ops.conv_fwd_raw(plan, x, y, s, graph, out)
+    ops.conv_fwd_raw(plan_fwd, x, y, s, graph, out)
     dm = (2 * out).contiguous()
 
-    names = ("fwd", "bwd_edges", "bwd_tail", "bwd_dx")
+    # under SENDER ordering the backward is one call (no per-pass entry point): it is reported as "bwd_edges"
+    names = ("fwd", "bwd_edges") if by_sender else ("fwd", "bwd_edges", "bwd_tail", "bwd_dx")
 
     def step(events=None):
         marks = []
@@ -239,9 +259,12 @@ def run_ours(args):
                 marks.append(ev)
 
         mark()
-        ops.conv_fwd_raw(plan, x, y, s, graph, out)
+        ops.conv_fwd_raw(plan_fwd, x, y, s, graph, out)
         mark()
-        if events is None:
+        if by_sender:
+            ops.conv_bwd_by_sender_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds))
+            mark()
+        elif events is None:
             ops.conv_bwd_raw(plan, x, y, s, dm, graph, ws, (dx, dy, ds))
         else:  # the three passes of the backward one by one, to time them
             for ph in (1, 2, 4):
@@ -357,11 +380,13 @@ def run_ours(args):
     ms_step = ms_total / args.steps
     peak, peak_kind = load_peaks()
     alg = algorithmic_bytes(e_real, g.num_real_nodes or n, X, Y, Z, S, C)
-    dominant = max(("fwd", "bwd_edges", "bwd_dx"), key=lambda k: per_kernel[k])
+    if by_sender:  # one backward call: its three kernels together
+        alg = {"fwd": alg["fwd"], "bwd_edges": alg["bwd_edges"] + alg["bwd_dx"]}
+    dominant = max((k for k in ("fwd", "bwd_edges", "bwd_dx") if k in per_kernel), key=lambda k: per_kernel[k])
     achieved = alg[dominant] / (per_kernel[dominant] * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath):
+    if os.path.exists(tpath) and not by_sender:
         with open(tpath) as fh:
             traffic = json.load(fh).get(f"config{cfg}", {}).get(dominant)
     cpu = time_cpu(cfg, steps=10, warmup=1) if world == 1 and not args.no_cpu else None
@@ -371,6 +396,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(cfg), "nodes_per_gpu": n, "edges_per_gpu": e_real, "channels": C,
                    "variant": plan.variant, "parallelism": f"independent graphs x{world}", "launch": launch_mode,
+                   "graph_ordering": args.ordering,
                    "l2": "inputs larger than L2 (s and ds are %.0f MB each)" % (s.numel() * 4 / 1e6)},
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
@@ -708,6 +734,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
+    ap.add_argument("--ordering", default="RECEIVER", choices=["RECEIVER", "SENDER"],
+                    help="N = 1: graph ordering of the operator (SENDER: edges stored sorted by sender)")
     ap.add_argument("--no-graph", action="store_true",
                     help="N = 1: issue the timed steps from Python instead of replaying a CUDA graph of one step")
     ap.add_argument("--window-edges", type=int, default=1 << 20, help="config 4: edges per window")

@@ -21,7 +21,9 @@ forward   one CTA per receiver, NW warps; warp g owns the paths of group g (path
           (b) forms each pair weight w[z,j] = sum_k val * y[k] in registers right
           where it is used (values are kernel parameters, i.e. constant-bank
           operands), (c) runs the unrolled multiply-adds
-          t[z] = sum_j w[z,j] x[j];  acc[z] += s[path] * t[z].
+          t[z] = sum_j w[z,j] x[j];  acc[z] += s[path] * t[z]
+          or, for a path with more output rows than x rows,
+          u[j] = s[path] * x[j];  acc[z] += sum_j w[z,j] u[j].
 backward  one CTA per receiver, NW warps; the receiver's cotangent rows dm[r] are
           staged in shared memory once; each warp then takes whole edges
           (e0 + warp, e0 + warp + NW, ...) and for each computes
@@ -51,10 +53,11 @@ VARIANTS = [
     # fsplit / bsplit = 1 launches one kernel per forward group / backward chunk, so that each
     # kernel's loop stays small enough for the instruction cache
     # fw = warps per CTA of a split forward kernel; gbuf = 2 double-buffers the staged dm rows
+    # uform = 1: forward paths with more output rows than x rows scale the x rows by s first
     dict(id=1, name="l1l3", x="0e+1o", nw=2, rpc=2, nst=3, fmin=3, rot=0, fsplit=0, fw=4, bw=4, nslot=2, slot_rows=14,
-         bmin=2, bsplit=0, gbuf=2, fwd_groups=None),
+         bmin=2, bsplit=0, gbuf=2, fwd_groups=None, uform=1),
     dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=2, slot_rows=14,
-         bmin=2, bsplit=1, gbuf=2, fwd_groups=None),
+         bmin=2, bsplit=1, gbuf=2, fwd_groups=None, uform=1),
 ]
 Y_IRREPS = "0e+1o+2e+3o"
 OUT_FILTER = "0e+1o+2e+3o"

@@ -247,9 +247,11 @@ def conv_bwd_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch
     return dx, dy, ds
 
 
-def conv_bwd_by_sender_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch.Tensor | None = None):
+def conv_bwd_by_sender_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, workspace: torch.Tensor | None = None,
+                           out=None):
     """Backward for a `SENDER`-ordered graph (``e3j_b200_conv_bwd_by_sender``): dy, ds in stored
-    order, dx summed over each sender's stored segment."""
+    order, dx summed over each sender's stored segment.  ``out`` may hold preallocated
+    ``(dx, dy, ds)``."""
     if graph.ordering != "SENDER":
         raise ValueError("conv_bwd_by_sender_raw needs a graph built with ordering='SENDER'")
     dev = _require_cuda(x, y, s, dm, graph.sender, graph.receiver_ptr)
@@ -258,7 +260,7 @@ def conv_bwd_by_sender_raw(plan: ConvPlan, x, y, s, dm, graph: ConvGraph, worksp
     need = int(_lib.lib().e3j_b200_conv_bwd_workspace_bytes(plan.handle, n, e))
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         workspace = torch.empty(need, dtype=torch.uint8, device=dev)
-    dx, dy, ds = torch.empty_like(x), torch.empty_like(y), torch.empty_like(s)
+    dx, dy, ds = out if out is not None else (torch.empty_like(x), torch.empty_like(y), torch.empty_like(s))
     with torch.cuda.device(dev):
         _lib.check(
             _lib.lib().e3j_b200_conv_bwd_by_sender(
