@@ -211,8 +211,8 @@ def run_ours(args):
 
     cfg = args.config
     by_sender = args.ordering == "SENDER"
-    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering=args.ordering,
-                       avg_num_neighbors=30.0)  # fmt: skip
+    conv = Convolution((args.x_irreps or problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER,
+                       graph_ordering=args.ordering, avg_num_neighbors=30.0)  # fmt: skip
     g = problems.make_graph(cfg, seed=rank, num_nodes=args.nodes)
     x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
     X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
@@ -386,7 +386,7 @@ def run_ours(args):
     achieved = alg[dominant] / (per_kernel[dominant] * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath) and not by_sender:
+    if os.path.exists(tpath) and not by_sender and not args.x_irreps:
         with open(tpath) as fh:
             traffic = json.load(fh).get(f"config{cfg}", {}).get(dominant)
     cpu = time_cpu(cfg, steps=10, warmup=1) if world == 1 and not args.no_cpu else None
@@ -394,7 +394,8 @@ def run_ours(args):
         "metric": METRIC, "value": edges_all / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "nodes_per_gpu": n, "edges_per_gpu": e_real, "channels": C,
+        "config": {"workload": workload_name(cfg) + (f" [x irreps overridden: {args.x_irreps}]" if args.x_irreps else ""),
+                   "nodes_per_gpu": n, "edges_per_gpu": e_real, "channels": C,
                    "variant": plan.variant, "parallelism": f"independent graphs x{world}", "launch": launch_mode,
                    "graph_ordering": args.ordering,
                    "l2": "inputs larger than L2 (s and ds are %.0f MB each)" % (s.numel() * 4 / 1e6)},
@@ -734,6 +735,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
+    ap.add_argument("--x-irreps", default=None,
+                    help="N = 1: node-feature irreps instead of the configuration's (e.g. 0e, 0e+1o+2e), same graph")
     ap.add_argument("--ordering", default="RECEIVER", choices=["RECEIVER", "SENDER"],
                     help="N = 1: graph ordering of the operator (SENDER: edges stored sorted by sender)")
     ap.add_argument("--no-graph", action="store_true",

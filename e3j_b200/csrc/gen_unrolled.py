@@ -58,6 +58,11 @@ VARIANTS = [
          bmin=2, bsplit=0, gbuf=2, fwd_groups=None, uform=1),
     dict(id=2, name="l3l3", x="0e+1o+2e+3o", nw=4, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=2, slot_rows=14,
          bmin=2, bsplit=1, gbuf=2, fwd_groups=None, uform=1),
+    # scalar node features (first interaction layer) and the l <= 2 hidden layer
+    dict(id=3, name="l0l3", x="0e", nw=1, rpc=4, nst=3, fmin=4, rot=0, fsplit=0, fw=4, bw=4, nslot=2, slot_rows=14,
+         bmin=3, bsplit=0, gbuf=2, fwd_groups=None, uform=1),
+    dict(id=4, name="l2l3", x="0e+1o+2e", nw=3, rpc=1, nst=3, fmin=2, rot=0, fsplit=1, fw=4, bw=4, nslot=2, slot_rows=14,
+         bmin=2, bsplit=1, gbuf=2, fwd_groups=None, uform=1),
 ]
 Y_IRREPS = "0e+1o+2e+3o"
 OUT_FILTER = "0e+1o+2e+3o"

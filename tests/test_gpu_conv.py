@@ -350,3 +350,31 @@ def test_check_graph_reports_and_rejects():
     too_long = ops.ConvGraph(n, graph.sender[:100].contiguous(), graph.receiver, graph.receiver_ptr)
     with pytest.raises(_lib.E3JError, match="InvalidArgument"):
         ops.check_graph(too_long)  # offsets beyond the 100 edges given
+
+
+@pytest.mark.parametrize("x_irreps,variant,nodes", [("0e", 3, 400), ("0e+1o+2e", 4, 300)])
+def test_more_unrolled_variants(x_irreps, variant, nodes):
+    """Scalar node features (first interaction layer) and the l <= 2 hidden layer have unrolled
+    kernels of their own; forward and backward against the oracle, and the table-driven kernels
+    on the same inputs."""
+    conv = Convolution((x_irreps, problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER", avg_num_neighbors=20.0)
+    g = problems.make_graph(2, seed=4, num_nodes=nodes)
+    inp = problems.make_inputs(g, 2, conv.num_scalars, conv.source[0].dim, seed=4)
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    rng = np.random.default_rng(0)
+    dm = rng.standard_normal((g.num_nodes, conv.target.dim, 128)).astype(np.float32)
+    (out, dx, dy, ds), plan = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, conv.target.dim, dm,
+                                      idx_dtype="uint8", poison=True)  # fmt: skip
+    assert plan.variant == variant
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    ptr_t, perm_t = c_oracle.transpose_csr(g.sender, g.num_nodes)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, g.sender, ptr, conv.target.dim), what="out")
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, inp.x, inp.y, inp.s, dm, g.sender, ptr, ptr_t, perm_t)
+    assert_close(dx, wdx, what="dx")
+    assert_close(dy, wdy, what="dy")
+    assert_close(ds, wds, what="ds")
+    (gout, gdx, gdy, gds), gplan = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, conv.target.dim, dm,
+                                           idx_dtype="uint8", force_generic=True)  # fmt: skip
+    assert gplan.variant == 0
+    for a, b, name in ((out, gout, "out"), (dx, gdx, "dx"), (dy, gdy, "dy"), (ds, gds, "ds")):
+        assert_close(a, b, what=name + " vs table-driven")
