@@ -216,7 +216,7 @@ def run_ours(args):
     g = problems.make_graph(cfg, seed=rank, num_nodes=args.nodes)
     x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
     X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
-    plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device)
+    plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device, args.table_driven)
     snd_h, rcv_h = g.sender, g.receiver
     if by_sender:
         # the same edges stored sorted by sender (padding stays last); the forward then runs over the
@@ -232,7 +232,7 @@ def run_ours(args):
         from e3j_b200.coef import Coef4D
 
         signed = Coef4D(conv.coef.val * conv.y_parity[conv.coef.idx[:, 2]], conv.coef.idx, idx_dtype=conv.coef.idx_dtype)
-        plan_fwd = ops.get_plan(signed.pack(), (X, Y, Z, S, C), device)
+        plan_fwd = ops.get_plan(signed.pack(), (X, Y, Z, S, C), device, args.table_driven)
     else:
         plan_fwd = plan
     graph = conv.prepare_graph(g.num_nodes, torch.as_tensor(snd_h).to(device), torch.as_tensor(rcv_h).to(device))
@@ -735,6 +735,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
+    ap.add_argument("--table-driven", action="store_true",
+                    help="N = 1: bypass the unrolled kernels (the path of tables that match no variant)")
     ap.add_argument("--x-irreps", default=None,
                     help="N = 1: node-feature irreps instead of the configuration's (e.g. 0e, 0e+1o+2e), same graph")
     ap.add_argument("--ordering", default="RECEIVER", choices=["RECEIVER", "SENDER"],

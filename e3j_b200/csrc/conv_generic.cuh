@@ -97,6 +97,69 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_kernel(
 }
 
 // ---------------------------------------------------------------------------
+// forward, four channels per thread (C a multiple of 4, 16-byte aligned operands)
+// ---------------------------------------------------------------------------
+// A row of threadIdx.y walks receivers; thread tx owns the channel quads tx, tx + blockDim.x, ...
+// The table is sorted by output row, so a thread sums the terms of one output row in
+// registers and adds the sum to the receiver's accumulator row (shared memory, one
+// read-modify-write per output row and edge).  x and s rows are re-read per table row
+// through L1 as 128-bit loads.
+__global__ void __launch_bounds__(kMaxThreadsX) conv_fwd_vec4_kernel(
+    DeviceTable table, bool table_in_smem, const float *__restrict__ x, const float *__restrict__ y,
+    const float *__restrict__ s, const int32_t *__restrict__ sender, const int32_t *__restrict__ receiver_ptr,
+    float *__restrict__ out, int32_t N, int32_t NS, Dims d) {
+    extern __shared__ __align__(16) float smem_raw[];
+    float *smem = smem_raw;
+    const SmemTable tab = stage_table(table, table_in_smem, smem);
+    const int QT = blockDim.x, tx = threadIdx.x;
+    const int Q = d.C / 4;  // channel quads per row
+    float4 *acc = reinterpret_cast<float4 *>(smem) + (size_t)threadIdx.y * d.Z * QT + tx;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; r < N;
+         r += (int64_t)gridDim.x * blockDim.y) {
+        const int32_t e0 = receiver_ptr[r], e1 = receiver_ptr[r + 1];
+        for (int q = tx; q < Q; q += QT) {
+            for (int z = 0; z < d.Z; z++) acc[z * QT] = zero4;
+            for (int32_t e = e0; e < e1; e++) {
+                const int32_t a = sender[e];
+                if (!in_range(a, NS)) continue;
+                const float4 *xa = reinterpret_cast<const float4 *>(x + ((int64_t)a * d.X) * d.C) + q;
+                const float4 *se = reinterpret_cast<const float4 *>(s + ((int64_t)e * d.S) * d.C) + q;
+                const float *ye = y + (int64_t)e * d.Y;
+                int cur = -1;
+                float4 run = zero4;
+                for (int n = 0; n < table.nnz; n++) {
+                    const int4 id = tab.idx[n];
+                    if (id.x != cur) {
+                        if (cur >= 0) {
+                            float4 v = acc[cur * QT];
+                            v.x += run.x; v.y += run.y; v.z += run.z; v.w += run.w;
+                            acc[cur * QT] = v;
+                        }
+                        cur = id.x;
+                        run = zero4;
+                    }
+                    const float w = tab.val[n] * ye[id.z];
+                    const float4 xv = xa[(int64_t)id.y * Q], sv = se[(int64_t)id.w * Q];
+                    run.x = fmaf(w, xv.x * sv.x, run.x);
+                    run.y = fmaf(w, xv.y * sv.y, run.y);
+                    run.z = fmaf(w, xv.z * sv.z, run.z);
+                    run.w = fmaf(w, xv.w * sv.w, run.w);
+                }
+                if (cur >= 0) {
+                    float4 v = acc[cur * QT];
+                    v.x += run.x; v.y += run.y; v.z += run.z; v.w += run.w;
+                    acc[cur * QT] = v;
+                }
+            }
+            float4 *o = reinterpret_cast<float4 *>(out + (r * d.Z) * d.C) + q;
+            for (int z = 0; z < d.Z; z++) o[(int64_t)z * Q] = acc[z * QT];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // backward, pass 1: per receiver, per edge -> ds[e], dy[e] and the edge's dx message
 // ---------------------------------------------------------------------------
 // Shared memory per receiver row: ds[S*CT] | dxm[X*CT] | dy[Y*CT] | warp partials [4*Y].
@@ -164,6 +227,93 @@ __global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_kernel(
             }
             if (one_warp) __syncwarp(); else __syncthreads();
             for (int k = tx; k < d.Y; k += CT) {
+                float v = 0.f;
+                for (int w = 0; w < nwarp; w++) v += dy_warp[w * d.Y + k];
+                dy[(int64_t)e * d.Y + k] = v;
+            }
+            if (one_warp) __syncwarp(); else __syncthreads();
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// backward, pass 1, four channels per thread (C a multiple of 4, 16-byte aligned operands)
+// ---------------------------------------------------------------------------
+// As conv_bwd_edges_kernel, with float4 accumulator rows: shared memory per row of threads
+//   ds[S][QT] float4 | dx[X][QT] float4 | dy[Y][QT] float | warp partials [nwarp * Y] float.
+__global__ void __launch_bounds__(kMaxThreadsX) conv_bwd_edges_vec4_kernel(
+    DeviceTable table, bool table_in_smem, const float *__restrict__ x, const float *__restrict__ y,
+    const float *__restrict__ s, const float *__restrict__ dm, const int32_t *__restrict__ sender,
+    const int32_t *__restrict__ receiver_ptr, const int32_t *__restrict__ edge_perm,
+    float *__restrict__ dxm, float *__restrict__ dy, float *__restrict__ ds, int32_t N, int32_t NS, Dims d) {
+    extern __shared__ __align__(16) float smem_raw[];
+    float *smem = smem_raw;
+    const SmemTable tab = stage_table(table, table_in_smem, smem);
+    const int QT = blockDim.x, tx = threadIdx.x, Q = d.C / 4;
+    const int per_row = (d.S + d.X) * QT * 4 + d.Y * QT + 4 * d.Y;
+    float *base = smem + (size_t)threadIdx.y * per_row;
+    float4 *ds_acc = reinterpret_cast<float4 *>(base) + tx;
+    float4 *dx_acc = ds_acc + d.S * QT;
+    float *dy_acc = base + (d.S + d.X) * QT * 4;
+    float *dy_warp = dy_acc + d.Y * QT;
+    const bool one_warp = (QT == 32);  // blockDim.y > 1 only in this case
+    const int lane = tx & 31, warp = tx >> 5, nwarp = (QT + 31) >> 5;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; r < N;
+         r += (int64_t)gridDim.x * blockDim.y) {
+        const int32_t e0 = receiver_ptr[r], e1 = receiver_ptr[r + 1];
+        const float4 *g = reinterpret_cast<const float4 *>(dm + (r * d.Z) * d.C);
+        for (int32_t p = e0; p < e1; p++) {
+            const int32_t e = edge_perm ? edge_perm[p] : p;
+            const int32_t a = sender[e];
+            const bool valid = in_range(a, NS);
+            for (int k = 0; k < d.Y; k++) dy_acc[k * QT + tx] = 0.f;
+            for (int q0 = 0; q0 < Q; q0 += QT) {
+                const int q = q0 + tx;
+                const bool act = q < Q;
+                for (int l = 0; l < d.S; l++) ds_acc[l * QT] = zero4;
+                for (int j = 0; j < d.X; j++) dx_acc[j * QT] = zero4;
+                if (valid && act) {
+                    const float4 *xa = reinterpret_cast<const float4 *>(x + ((int64_t)a * d.X) * d.C) + q;
+                    const float4 *se = reinterpret_cast<const float4 *>(s + ((int64_t)e * d.S) * d.C) + q;
+                    const float *ye = y + (int64_t)e * d.Y;
+                    for (int n = 0; n < table.nnz; n++) {
+                        const int4 id = tab.idx[n];
+                        const float val = tab.val[n], yv = ye[id.z];
+                        const float4 gv = g[(int64_t)id.x * Q + q];
+                        const float4 xv = xa[(int64_t)id.y * Q], sv = se[(int64_t)id.w * Q];
+                        const float4 t = make_float4(val * gv.x, val * gv.y, val * gv.z, val * gv.w);
+                        float4 u = ds_acc[id.w * QT];
+                        u.x = fmaf(t.x * yv, xv.x, u.x); u.y = fmaf(t.y * yv, xv.y, u.y);
+                        u.z = fmaf(t.z * yv, xv.z, u.z); u.w = fmaf(t.w * yv, xv.w, u.w);
+                        ds_acc[id.w * QT] = u;
+                        float4 v = dx_acc[id.y * QT];
+                        v.x = fmaf(t.x * yv, sv.x, v.x); v.y = fmaf(t.y * yv, sv.y, v.y);
+                        v.z = fmaf(t.z * yv, sv.z, v.z); v.w = fmaf(t.w * yv, sv.w, v.w);
+                        dx_acc[id.y * QT] = v;
+                        float w = dy_acc[id.z * QT + tx];
+                        w = fmaf(t.x * sv.x, xv.x, w); w = fmaf(t.y * sv.y, xv.y, w);
+                        w = fmaf(t.z * sv.z, xv.z, w); w = fmaf(t.w * sv.w, xv.w, w);
+                        dy_acc[id.z * QT + tx] = w;
+                    }
+                }
+                if (act) {
+                    float4 *dse = reinterpret_cast<float4 *>(ds + ((int64_t)e * d.S) * d.C) + q;
+                    for (int l = 0; l < d.S; l++) dse[(int64_t)l * Q] = ds_acc[l * QT];
+                    float4 *dxe = reinterpret_cast<float4 *>(dxm + ((int64_t)e * d.X) * d.C) + q;
+                    for (int j = 0; j < d.X; j++) dxe[(int64_t)j * Q] = dx_acc[j * QT];
+                }
+            }
+            // channel reduction of dy: xor-butterfly inside each warp, then warps in order
+            for (int k = 0; k < d.Y; k++) {
+                float v = dy_acc[k * QT + tx];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) dy_warp[warp * d.Y + k] = v;
+            }
+            if (one_warp) __syncwarp(); else __syncthreads();
+            for (int k = tx; k < d.Y; k += QT) {
                 float v = 0.f;
                 for (int w = 0; w < nwarp; w++) v += dy_warp[w * d.Y + k];
                 dy[(int64_t)e * d.Y + k] = v;

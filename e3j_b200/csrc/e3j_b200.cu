@@ -197,6 +197,27 @@ GenericGeometry generic_geometry(const e3j_b200_plan *p) {
     return g;
 }
 
+// Geometry of the four-channels-per-thread table-driven kernels: threads over channel quads.
+GenericGeometry generic_geometry_vec4(const e3j_b200_plan *p) {
+    GenericGeometry g = generic_geometry(p);
+    const int qt = std::min(generic::kMaxThreadsX, ((p->d.C / 4 + 31) / 32) * 32);
+    g.block = dim3(qt, qt == 32 ? 4 : 1, 1);
+    return g;
+}
+
+bool vec4_ok(const e3j_b200_plan *p, std::initializer_list<const void *> ptrs) {
+    if (p->d.C % 4) return false;
+    for (const void *q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) % 16) return false;
+    return true;
+}
+
+size_t bwd_vec4_smem(const e3j_b200_plan *p) {
+    const GenericGeometry g = generic_geometry_vec4(p);
+    const size_t per_row = ((size_t)(p->d.S + p->d.X) * g.block.x * 4 + (size_t)p->d.Y * g.block.x + 4 * p->d.Y) * sizeof(float);
+    return g.table_bytes + per_row * g.block.y;
+}
+
 int check_common(const e3j_b200_plan *p, int32_t N, int64_t E) {
     if (!p) return set_error(E3J_B200_INVALID_ARGUMENT, "plan is null");
     if (N < 0 || E < 0) return set_error(E3J_B200_INVALID_ARGUMENT, "negative graph size");
@@ -233,6 +254,23 @@ int e3j_b200_conv_fwd_rect(const e3j_b200_plan *p, const float *x, const float *
         return unrolled::launch_fwd(p->variant, p->un, p->lim.sm_count, x, y, s, sender,
                                     receiver_ptr, out, N, NS, E, debug, stream);
 
+    DeviceTable t{p->d_val, p->d_idx, p->nnz};
+    if (vec4_ok(p, {x, s, out})) {
+        // four channels per thread; as many receiver rows per block (of one warp) as shared memory takes
+        GenericGeometry g = generic_geometry_vec4(p);
+        const size_t row_bytes = (size_t)p->d.Z * g.block.x * sizeof(float4);
+        while (g.block.y > 1 && g.table_bytes + g.block.y * row_bytes > 96 * 1024) g.block.y /= 2;
+        const size_t smem = g.table_bytes + g.block.y * row_bytes;
+        if (smem <= (size_t)p->lim.smem_optin) {
+            if (smem > 48 * 1024)
+                E3JB_CUDA_TRY(cudaFuncSetAttribute(generic::conv_fwd_vec4_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            const int grid = (int)std::min<int64_t>(ceil_div64(N, g.block.y), (int64_t)p->lim.sm_count * 16);
+            generic::conv_fwd_vec4_kernel<<<grid, g.block, smem, stream>>>(t, g.table_in_smem, x, y, s, sender,
+                                                                          receiver_ptr, out, N, NS, p->d);
+            return check_launch("convolution", debug, stream);
+        }
+    }
     const GenericGeometry g = generic_geometry(p);
     const size_t acc_bytes = (size_t)g.block.y * p->d.Z * g.block.x * sizeof(float);
     const bool acc_in_smem = g.table_bytes + acc_bytes <= (size_t)p->lim.smem_optin;
@@ -242,7 +280,6 @@ int e3j_b200_conv_fwd_rect(const e3j_b200_plan *p, const float *x, const float *
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int64_t want = ceil_div64(N, g.block.y);
     const int grid = (int)std::min<int64_t>(want, (int64_t)p->lim.sm_count * 16);
-    DeviceTable t{p->d_val, p->d_idx, p->nnz};
     generic::conv_fwd_kernel<<<grid, g.block, smem, stream>>>(t, g.table_in_smem, acc_in_smem, x, y,
                                                               s, sender, receiver_ptr, out, N, NS, p->d);
     return check_launch("convolution", debug, stream);
@@ -368,6 +405,18 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
         if (p->variant != E3J_B200_VARIANT_GENERIC) {
             rc = unrolled::launch_bwd_edges(p->variant, p->un, p->lim.sm_count, x, y0, s0, dm, sender0,
                                             receiver_ptr, edge_perm, dxm0, dy_part0, ds0, N, NS, E, debug, stream);
+            if (rc) return rc;
+        } else if (vec4_ok(p, {x, s, dm, dxm, ds}) && bwd_vec4_smem(p) <= (size_t)p->lim.smem_optin) {
+            const GenericGeometry g = generic_geometry_vec4(p);
+            const size_t smem = bwd_vec4_smem(p);
+            if (smem > 48 * 1024)
+                E3JB_CUDA_TRY(cudaFuncSetAttribute(generic::conv_bwd_edges_vec4_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            const int grid = (int)std::min<int64_t>(ceil_div64(N, g.block.y), (int64_t)p->lim.sm_count * 16);
+            DeviceTable t{p->d_val, p->d_idx, p->nnz};
+            generic::conv_bwd_edges_vec4_kernel<<<grid, g.block, smem, stream>>>(
+                t, g.table_in_smem, x, y0, s0, dm, sender0, receiver_ptr, edge_perm, dxm0, dy0, ds0, N, NS, d);
+            rc = check_launch("convolution_bwd (edges)", debug, stream);
             if (rc) return rc;
         } else {
             const GenericGeometry g = generic_geometry(p);
