@@ -469,15 +469,20 @@ __global__ void __launch_bounds__(256) dx_reduce_window_kernel(const float *__re
     for (int64_t a = warp; a < N; a += nwarps) {
         const int32_t p0 = sender_ptr_t[a], p1 = sender_ptr_t[a + 1];
         int below0 = 0, below1 = 0;
-        for (int32_t p = p0 + lane; p < p1; p += 32) {
-            const int64_t e = perm_t[p];
-            below0 += e < e0;
-            below1 += e < e1;
-        }
+        // the segment is ascending: its ends tell whether it meets the window at all
+        const bool meets = p0 < p1 && perm_t[p1 - 1] >= e0 && perm_t[p0] < e1;
+        if (!meets && accumulate) continue;
+        if (meets) {
+            for (int32_t p = p0 + lane; p < p1; p += 32) {
+                const int64_t e = perm_t[p];
+                below0 += e < e0;
+                below1 += e < e1;
+            }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            below0 += __shfl_xor_sync(0xffffffffu, below0, o);
-            below1 += __shfl_xor_sync(0xffffffffu, below1, o);
+            for (int o = 16; o > 0; o >>= 1) {
+                below0 += __shfl_xor_sync(0xffffffffu, below0, o);
+                below1 += __shfl_xor_sync(0xffffffffu, below1, o);
+            }
         }
         const int32_t q0 = p0 + below0, q1 = p0 + below1;
         if (q0 == q1 && accumulate) continue;
