@@ -722,6 +722,57 @@ def run_ours_config4(args, world, rank, local, device):
         dist.destroy_process_group()
 
 
+def run_tensor_product(args):
+    """--op tensor_product: the standalone product on the edges of the configuration (x gathered per edge
+    beforehand, y the edge harmonics without a channel axis, OUTER mode), forward + cotangents."""
+    import torch
+
+    from e3j_b200 import problems
+    from e3j_b200.coef import Coef
+    from e3j_b200.ops_tensor_product import CUDATensorProductParams, tensor_product
+    from e3j_b200.tensor_product import TensorProduct
+
+    cfg = args.config
+    device = torch.device("cuda", 0)
+    tp = TensorProduct((args.x_irreps or problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER)
+    g = problems.make_graph(cfg, seed=0, num_nodes=args.nodes)
+    rows, X, Y, Z, C = int(g.num_real_edges), tp.source[0].dim, tp.source[1].dim, tp.target.dim, 128
+    coef = Coef(tp.values.astype(np.float32), tp.indices.astype(np.int32)).pack()
+    gen = torch.Generator(device=device).manual_seed(0)
+    x = torch.randn((rows, X, C), generator=gen, device=device, requires_grad=True)
+    y = torch.randn((rows, Y), generator=gen, device=device, requires_grad=True)
+    params = CUDATensorProductParams(Z, "OUTER")
+    dz = torch.randn((rows, Z, C), generator=gen, device=device)
+
+    def step():
+        x.grad = y.grad = None
+        tensor_product(coef, x, y, params).backward(dz)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(1, min(args.steps, 20))
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    peak, peak_kind = load_peaks()
+    alg = 4 * rows * (2 * X * C + 2 * Y + 2 * Z * C) + 4 * rows * (X * C + Y)  # fwd r/w + bwd reads + dx, dy writes
+    print(json.dumps({
+        "metric": "tensor_product_fwd_vjp_rows_per_s", "value": rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1,
+        "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
+        "data": "synthetic", "vs_baseline": None,
+        "config": {"workload": f"standalone tensor product, OUTER, rows = edges of config {cfg} ({rows}), X={X} Y={Y} Z={Z} C={C}",
+                   "l2": "operands larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "tp fwd + dx + dy (table-driven)", "achieved": alg / (ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": alg / (ms * 1e-3) / 1e9 / peak, "traffic": None,
+                     "peak_source": peak_kind},
+    }))  # fmt: skip
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -735,6 +786,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--producer", default="tf32x3", choices=["fp32", "tf32x3"],
                     help="config 4: arithmetic of the radial MLP's wide layer (see e3j_b200.chunked.RadialProducer)")
+    ap.add_argument("--op", default="convolution", choices=["convolution", "tensor_product"],
+                    help="tensor_product: time the standalone product (not the headline metric)")
     ap.add_argument("--table-driven", action="store_true",
                     help="N = 1: bypass the unrolled kernels (the path of tables that match no variant)")
     ap.add_argument("--x-irreps", default=None,
@@ -748,6 +801,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.op == "tensor_product":
+        run_tensor_product(args)
     else:
         run_ours(args)
 

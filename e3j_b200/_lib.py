@@ -148,6 +148,14 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_csr_transpose_workspace_bytes.argtypes = [i32, i64]
     lib.e3j_b200_csr_transpose.restype = c.c_int
     lib.e3j_b200_csr_transpose.argtypes = [vp, i64, i32, vp, vp, vp, c.c_size_t, vp]
+    lib.e3j_b200_tp_plan_create.restype = c.c_int
+    lib.e3j_b200_tp_plan_create.argtypes = [vp, i32, i32, i32, i32, i32, c.POINTER(vp)]
+    lib.e3j_b200_tp_plan_destroy.restype = None
+    lib.e3j_b200_tp_plan_destroy.argtypes = [vp]
+    lib.e3j_b200_tensor_product.restype = c.c_int
+    lib.e3j_b200_tensor_product.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, vp]
+    lib.e3j_b200_tensor_product_bwd.restype = c.c_int
+    lib.e3j_b200_tensor_product_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp]
     lib.e3j_b200_check_graph.restype = c.c_int
     lib.e3j_b200_check_graph.argtypes = [vp, vp, i32, i32, i64, c.POINTER(c.c_int32), vp]
     lib.e3j_b200_csr_untranspose.restype = c.c_int
@@ -186,6 +194,10 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_csr_transpose",
     "e3j_b200_csr_untranspose",
     "e3j_b200_check_graph",
+    "e3j_b200_tp_plan_create",
+    "e3j_b200_tp_plan_destroy",
+    "e3j_b200_tensor_product",
+    "e3j_b200_tensor_product_bwd",
     "e3j_b200_harmonics_fwd",
     "e3j_b200_harmonics_bwd",
 )

@@ -11,6 +11,7 @@
 #include "conv_unrolled.cuh"
 #include "csr.cuh"
 #include "harmonics.cuh"
+#include "tensor_product.cuh"
 
 namespace e3jb {
 
@@ -540,6 +541,116 @@ int e3j_b200_check_graph(const int32_t *sender, const int32_t *receiver_ptr, int
         return set_error(E3J_B200_INVALID_ARGUMENT, msg);
     }
     return E3J_B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// standalone tensor product on rows
+// ---------------------------------------------------------------------------
+struct e3j_b200_tp_plan {
+    int32_t X = 0, Y = 0, Z = 0, nnz = 0;
+    float *d_val[3] = {nullptr, nullptr, nullptr};  // table sorted by i, by j, by k
+    int4 *d_idx[3] = {nullptr, nullptr, nullptr};
+};
+
+void e3j_b200_tp_plan_destroy(e3j_b200_tp_plan *p) {
+    if (!p) return;
+    for (int o = 0; o < 3; o++) {
+        if (p->d_val[o]) cudaFree(p->d_val[o]);
+        if (p->d_idx[o]) cudaFree(p->d_idx[o]);
+    }
+    delete p;
+}
+
+int e3j_b200_tp_plan_create(const void *coef_host, int32_t nnz, int32_t idx_bytes, int32_t X, int32_t Y,
+                            int32_t Z, e3j_b200_tp_plan **plan_out) {
+    if (!plan_out) return set_error(E3J_B200_INVALID_ARGUMENT, "plan pointer is null");
+    *plan_out = nullptr;
+    if (nnz < 0 || (nnz > 0 && !coef_host)) return set_error(E3J_B200_INVALID_ARGUMENT, "coefficient table is null");
+    if (idx_bytes != 1 && idx_bytes != 4)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "unsupported (IDX, VAL) dtype pair");
+    if (X <= 0 || Y <= 0 || Z <= 0) return set_error(E3J_B200_INVALID_ARGUMENT, "dimensions must be positive");
+    struct Row { float val; int32_t i, j, k; };
+    std::vector<Row> rows(nnz);
+    const size_t row_bytes = idx_bytes == 1 ? 8 : 16;  // next_pow2(4 + 3 * idx_bytes)
+    const auto *bytes = static_cast<const unsigned char *>(coef_host);
+    for (int32_t n = 0; n < nnz; n++) {
+        const unsigned char *r = bytes + n * row_bytes;
+        Row t;
+        std::memcpy(&t.val, r, 4);
+        if (idx_bytes == 1) {
+            t.i = r[4]; t.j = r[5]; t.k = r[6];
+        } else {
+            int32_t q[3];
+            std::memcpy(q, r + 4, 12);
+            t.i = q[0]; t.j = q[1]; t.k = q[2];
+        }
+        if (t.i < 0 || t.i >= Z || t.j < 0 || t.j >= X || t.k < 0 || t.k >= Y)
+            return set_error(E3J_B200_INVALID_ARGUMENT, "coefficient row " + std::to_string(n) + " indexes out of bounds");
+        rows[n] = t;
+    }
+    auto *p = new e3j_b200_tp_plan();
+    p->X = X; p->Y = Y; p->Z = Z; p->nnz = nnz;
+    for (int o = 0; o < 3; o++) {
+        std::vector<Row> sorted(rows);
+        std::stable_sort(sorted.begin(), sorted.end(), [o](const Row &a, const Row &b) {
+            return o == 0 ? a.i < b.i : (o == 1 ? a.j < b.j : a.k < b.k);
+        });
+        std::vector<float> val(std::max(nnz, 1));
+        std::vector<int4> idx(std::max(nnz, 1));
+        for (int32_t n = 0; n < nnz; n++) {
+            val[n] = sorted[n].val;
+            idx[n] = make_int4(sorted[n].i, sorted[n].j, sorted[n].k, 0);
+        }
+        cudaError_t e = cudaMalloc(&p->d_val[o], val.size() * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&p->d_idx[o], idx.size() * sizeof(int4));
+        if (e == cudaSuccess) e = cudaMemcpy(p->d_val[o], val.data(), val.size() * sizeof(float), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(p->d_idx[o], idx.data(), idx.size() * sizeof(int4), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            e3j_b200_tp_plan_destroy(p);
+            return set_error(E3J_B200_CUDA_RUNTIME, std::string("tensor product plan: ") + cudaGetErrorString(e));
+        }
+    }
+    *plan_out = p;
+    return E3J_B200_OK;
+}
+
+static int tp_shape(const e3j_b200_tp_plan *p, int64_t rows, int32_t CX, int32_t CY, int32_t mode, tp::Shape &sh) {
+    if (!p) return set_error(E3J_B200_INVALID_ARGUMENT, "plan is null");
+    if (rows < 0 || CX <= 0 || CY <= 0) return set_error(E3J_B200_INVALID_ARGUMENT, "bad tensor product sizes");
+    if (mode == tp::INNER) return set_error(E3J_B200_UNIMPLEMENTED, "tensor product mode INNER");
+    if (mode != tp::OUTER && mode != tp::MAP) return set_error(E3J_B200_INVALID_ARGUMENT, "unknown tensor product mode");
+    if (mode == tp::MAP && CX != CY)
+        return set_error(E3J_B200_INVALID_ARGUMENT, "mode MAP needs as many RHS channels as LHS channels");
+    if (mode == tp::OUTER && CY == 1 && p->Y > tp::kMaxY)
+        return set_error(E3J_B200_UNIMPLEMENTED, "tensor product: more than 64 RHS rows without channels");
+    sh = tp::Shape{p->X, p->Y, p->Z, CX, CY, mode == tp::MAP ? CX : CX * CY, mode};
+    return E3J_B200_OK;
+}
+
+int e3j_b200_tensor_product(const e3j_b200_tp_plan *p, const float *x, const float *y, float *out, int64_t rows,
+                            int32_t CX, int32_t CY, int32_t mode, e3j_b200_stream stream) {
+    tp::Shape sh;
+    int rc = tp_shape(p, rows, CX, CY, mode, sh);
+    if (rc || rows == 0) return rc;
+    if (!x || !y || !out) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    const int grid = (int)std::min<int64_t>(rows, 148 * 16);
+    tp::fwd_kernel<<<grid, tp::kThreads, 0, stream>>>(tp::Table{p->d_val[0], p->d_idx[0], p->nnz}, x, y, out, rows, sh);
+    return check_launch("tensor_product", 0, stream);
+}
+
+int e3j_b200_tensor_product_bwd(const e3j_b200_tp_plan *p, const float *x, const float *y, const float *dz,
+                                float *dx, float *dy, int64_t rows, int32_t CX, int32_t CY, int32_t mode,
+                                e3j_b200_stream stream) {
+    tp::Shape sh;
+    int rc = tp_shape(p, rows, CX, CY, mode, sh);
+    if (rc || rows == 0) return rc;
+    if (!x || !y || !dz || !dx || !dy) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
+    const int grid = (int)std::min<int64_t>(rows, 148 * 16);
+    tp::bwd_dx_kernel<<<grid, tp::kThreads, 0, stream>>>(tp::Table{p->d_val[1], p->d_idx[1], p->nnz}, y, dz, dx, rows, sh);
+    rc = check_launch("tensor_product_bwd (dx)", 0, stream);
+    if (rc) return rc;
+    tp::bwd_dy_kernel<<<grid, tp::kThreads, 0, stream>>>(tp::Table{p->d_val[2], p->d_idx[2], p->nnz}, x, dz, dy, rows, sh);
+    return check_launch("tensor_product_bwd (dy)", 0, stream);
 }
 
 // ---------------------------------------------------------------------------

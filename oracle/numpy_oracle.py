@@ -77,3 +77,30 @@ def conv_bwd(val, idx4, x, y, s, dm, sender, receiver, *, dtype=np.float64, chun
         dy[e] = np.einsum("kn,en->ek", sk, np.sum(g * xj * slv, axis=-1))
         ds[e] = np.einsum("ln,enc->elc", sl, g * xj * yk)
     return dx, dy, ds
+
+
+def tensor_product(val, idx3, x, y, num_out, mode="OUTER"):
+    """Standalone tensor product on rows, float64 (src/e3j/core/tensor_product.py:300-319 with the
+    channel rules of src/e3j/utils/options.py:154-168): x (n, X, CX), y (n, Y, CY) ->
+    OUTER (n, Z, CX * CY), MAP (n, Z, C)."""
+    dense = np.zeros((num_out, x.shape[1], y.shape[1]))
+    for v, (i, j, k) in zip(val, idx3):
+        dense[i, j, k] += float(v)
+    x, y = x.astype(np.float64), y.astype(np.float64)
+    if mode == "MAP":
+        return np.einsum("ijk,njc,nkc->nic", dense, x, y)
+    out = np.einsum("ijk,nju,nkv->niuv", dense, x, y)
+    return out.reshape(out.shape[0], num_out, -1)
+
+
+def tensor_product_vjp(val, idx3, x, y, dz, mode="OUTER"):
+    """Cotangents (dx, dy) of :func:`tensor_product` for the cotangent dz of its output."""
+    num_out = dz.shape[1]
+    dense = np.zeros((num_out, x.shape[1], y.shape[1]))
+    for v, (i, j, k) in zip(val, idx3):
+        dense[i, j, k] += float(v)
+    x, y, dz = x.astype(np.float64), y.astype(np.float64), dz.astype(np.float64)
+    if mode == "MAP":
+        return np.einsum("ijk,nic,nkc->njc", dense, dz, y), np.einsum("ijk,nic,njc->nkc", dense, dz, x)
+    g = dz.reshape(dz.shape[0], num_out, x.shape[2], y.shape[2])
+    return np.einsum("ijk,niuv,nkv->nju", dense, g, y), np.einsum("ijk,niuv,nju->nkv", dense, g, x)

@@ -1,0 +1,71 @@
+"""Standalone tensor product on rows (TRAILING_CHANNELS; OUTER and MAP) against the float64
+restatement of the dense formulation, forward and cotangents."""
+
+import numpy as np
+import pytest
+import torch
+
+from e3j_b200.coef import Coef
+from e3j_b200.ops_tensor_product import CUDATensorProductParams, tensor_product
+from e3j_b200.tensor_product import TensorProduct
+from oracle import numpy_oracle
+from tests.conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _table(rng, nnz, nx, ny, nz):
+    idx = np.unique(np.stack([rng.integers(0, nz, nnz), rng.integers(0, nx, nnz), rng.integers(0, ny, nnz)], axis=-1), axis=0)
+    return rng.standard_normal(len(idx)).astype(np.float32), idx.astype(np.int32)
+
+
+@pytest.mark.parametrize("idx_dtype", ["uint8", "int32"])
+@pytest.mark.parametrize("mode,cx,cy", [("OUTER", 128, 1), ("OUTER", 8, 4), ("OUTER", 3, 5), ("MAP", 64, 64), ("MAP", 5, 5)])
+def test_random_tables(mode, cx, cy, idx_dtype):
+    rng = np.random.default_rng(cx * 31 + cy)
+    rows, nx, ny, nz = 37, 5, 4, 7  # output row 6 may get no entry: must come out as zeros
+    val, idx = _table(rng, 40, nx, ny, nz - 1)
+    x = rng.standard_normal((rows, nx, cx)).astype(np.float32)
+    y = rng.standard_normal((rows, ny, cy)).astype(np.float32)
+    coef = Coef(val, idx, idx_dtype=idx_dtype).pack()
+    tx, ty = torch.tensor(x, device=DEV, requires_grad=True), torch.tensor(y, device=DEV, requires_grad=True)
+    out = tensor_product(coef, tx, ty, CUDATensorProductParams(nz, mode))
+    want = numpy_oracle.tensor_product(val, idx, x, y, nz, mode)
+    assert_close(out.detach().cpu().numpy(), want, what="out")
+    assert not out.detach()[:, nz - 1].any()
+    dz = rng.standard_normal(want.shape).astype(np.float32)
+    out.backward(torch.tensor(dz, device=DEV))
+    wdx, wdy = numpy_oracle.tensor_product_vjp(val, idx, x, y, dz, mode)
+    assert_close(tx.grad.cpu().numpy(), wdx, what="dx")
+    assert_close(ty.grad.cpu().numpy(), wdy, what="dy")
+    # bitwise reproducible
+    out2 = tensor_product(coef, tx.detach(), ty.detach(), CUDATensorProductParams(nz, mode))
+    assert torch.equal(out2, out.detach())
+
+
+def test_clebsch_gordan_table_with_leading_axes_and_y_without_channels():
+    """Node features times edge harmonics, the product inside the convolution: x (B, E, X, C),
+    y (B, E, Y) without a channel axis."""
+    tp = TensorProduct(("0e+1o", "0e+1o+2e"), "0e+1o+2e")
+    val, idx = tp.values.astype(np.float32), tp.indices.astype(np.int32)
+    rng = np.random.default_rng(1)
+    b, e, c = 2, 50, 128
+    x = rng.standard_normal((b, e, tp.source[0].dim, c)).astype(np.float32)
+    y = rng.standard_normal((b, e, tp.source[1].dim)).astype(np.float32)
+    out = tensor_product(Coef(val, idx).pack(), torch.tensor(x, device=DEV), torch.tensor(y, device=DEV),
+                         CUDATensorProductParams(tp.target.dim, "OUTER"))  # fmt: skip
+    assert out.shape == (b, e, tp.target.dim, c)
+    want = numpy_oracle.tensor_product(val, idx, x.reshape(b * e, -1, c), y.reshape(b * e, -1, 1), tp.target.dim)
+    assert_close(out.cpu().numpy().reshape(b * e, tp.target.dim, c), want, what="out")
+
+
+def test_unsupported_modes_and_layouts_are_refused():
+    coef = Coef(np.ones(1, np.float32), np.zeros((1, 3), np.int32)).pack()
+    x, y = torch.zeros((2, 1, 4), device=DEV), torch.zeros((2, 1, 4), device=DEV)
+    with pytest.raises(NotImplementedError):
+        tensor_product(coef, x, y, CUDATensorProductParams(1, "INNER"))
+    with pytest.raises(NotImplementedError):
+        tensor_product(coef, x, y, CUDATensorProductParams(1, "OUTER", "LEADING_CHANNELS"))
+    with pytest.raises(NotImplementedError):
+        tensor_product(coef, x, torch.zeros((2, 1, 3), device=DEV), CUDATensorProductParams(1, "MAP"))
