@@ -156,6 +156,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.e3j_b200_tensor_product.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, vp]
     lib.e3j_b200_tensor_product_bwd.restype = c.c_int
     lib.e3j_b200_tensor_product_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp]
+    lib.e3j_b200_scatter_add_1_workspace_bytes.restype = c.c_size_t
+    lib.e3j_b200_scatter_add_1_workspace_bytes.argtypes = [i64, i32]
+    lib.e3j_b200_scatter_add_1.restype = c.c_int
+    lib.e3j_b200_scatter_add_1.argtypes = [vp, vp, vp, i64, i64, i32, vp, c.c_size_t, vp]
     lib.e3j_b200_check_graph.restype = c.c_int
     lib.e3j_b200_check_graph.argtypes = [vp, vp, i32, i32, i64, c.POINTER(c.c_int32), vp]
     lib.e3j_b200_csr_untranspose.restype = c.c_int
@@ -194,6 +198,8 @@ EXPORTED_SYMBOLS = (
     "e3j_b200_csr_transpose",
     "e3j_b200_csr_untranspose",
     "e3j_b200_check_graph",
+    "e3j_b200_scatter_add_1_workspace_bytes",
+    "e3j_b200_scatter_add_1",
     "e3j_b200_tp_plan_create",
     "e3j_b200_tp_plan_destroy",
     "e3j_b200_tensor_product",

@@ -126,6 +126,22 @@ __global__ void check_graph_kernel(const int32_t *__restrict__ sender, const int
     if (tid == 0) report[2] = (int32_t)min((int64_t)0x7fffffff, E - covered);
 }
 
+// out[r, o] = sum over the positions p of segment o of val[r, perm[p]], in segment order: the
+// scatter-add of the last axis of `val` by a 1-D index, as a gather (no atomics, fixed order).
+// One thread per output element; blockIdx.y walks the rows.
+__global__ void segment_sum_last_kernel(const float *__restrict__ val, const int32_t *__restrict__ ptr,
+                                        const int32_t *__restrict__ perm, float *__restrict__ out, int64_t rows,
+                                        int64_t num_idx, int32_t num_out) {
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const float *vr = val + r * num_idx;
+        for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < num_out; o += (int64_t)gridDim.x * blockDim.x) {
+            float acc = 0.f;
+            for (int32_t p = ptr[o]; p < ptr[o + 1]; p++) acc += vr[perm[p]];
+            out[r * num_out + o] = acc;
+        }
+    }
+}
+
 __global__ void fill_i32_kernel(int32_t *__restrict__ dst, int64_t n, int32_t value) {
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
         dst[t] = value;

@@ -517,6 +517,32 @@ int e3j_b200_csr_untranspose(const int32_t *sender_ptr_t, const int32_t *perm_t,
     return check_launch("csr_untranspose", 0, stream);
 }
 
+size_t e3j_b200_scatter_add_1_workspace_bytes(int64_t num_idx, int32_t num_out) {
+    auto round = [](size_t b) { return (b + 255) / 256 * 256; };
+    return round(((size_t)std::max(num_out, 0) + 2) * sizeof(int32_t)) + round((size_t)std::max<int64_t>(num_idx, 1) * sizeof(int32_t)) +
+           e3j_b200_csr_transpose_workspace_bytes(num_out, num_idx);
+}
+
+int e3j_b200_scatter_add_1(const int32_t *idx, const float *val, float *out, int64_t rows, int64_t num_idx,
+                           int32_t num_out, void *workspace, size_t workspace_bytes, e3j_b200_stream stream) {
+    if (rows < 0 || num_idx < 0 || num_out < 0 || !out || (num_idx > 0 && (!idx || !val)))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "bad scatter_add_1 operands");
+    if (!workspace || workspace_bytes < e3j_b200_scatter_add_1_workspace_bytes(num_idx, num_out))
+        return set_error(E3J_B200_INVALID_ARGUMENT, "workspace is too small");
+    if (rows == 0 || num_out == 0) return E3J_B200_OK;
+    auto round = [](size_t b) { return (b + 255) / 256 * 256; };
+    char *base = static_cast<char *>(workspace);
+    int32_t *ptr = reinterpret_cast<int32_t *>(base);
+    int32_t *perm = reinterpret_cast<int32_t *>(base + round(((size_t)num_out + 2) * sizeof(int32_t)));
+    void *tws = base + round(((size_t)num_out + 2) * sizeof(int32_t)) + round((size_t)std::max<int64_t>(num_idx, 1) * sizeof(int32_t));
+    // stable grouping of the positions by destination: any order of idx is accepted, sums run in position order
+    int rc = e3j_b200_csr_transpose(idx, num_idx, num_out, ptr, perm, tws, e3j_b200_csr_transpose_workspace_bytes(num_out, num_idx), stream);
+    if (rc) return rc;
+    const dim3 grid((unsigned)std::min<int64_t>(ceil_div64(num_out, 128), 1024), (unsigned)std::min<int64_t>(rows, 65535));
+    csr::segment_sum_last_kernel<<<grid, 128, 0, stream>>>(val, ptr, perm, out, rows, num_idx, num_out);
+    return check_launch("scatter_add_1", 0, stream);
+}
+
 int e3j_b200_check_graph(const int32_t *sender, const int32_t *receiver_ptr, int32_t N, int32_t NS, int64_t E,
                          int32_t *report_host, e3j_b200_stream stream) {
     if (N < 0 || NS < 0 || E < 0 || !receiver_ptr || !report_host || (E > 0 && !sender))
@@ -614,6 +640,17 @@ int e3j_b200_tp_plan_create(const void *coef_host, int32_t nnz, int32_t idx_byte
     return E3J_B200_OK;
 }
 
+// rows whose operands and table fit this much shared memory take the staged kernels (several blocks per SM)
+static constexpr size_t kTpStagedSmem = 72 * 1024;
+
+// four channels per lane: CX a multiple of 4, MAP (CY == CX) or OUTER without RHS channels, 16-byte aligned operands
+static bool tp_vec4_ok(const tp::Shape &sh, std::initializer_list<const void *> ptrs) {
+    if (sh.CX % 4 || !(sh.mode == tp::MAP || sh.CY == 1)) return false;
+    for (const void *q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) % 16) return false;
+    return true;
+}
+
 static int tp_shape(const e3j_b200_tp_plan *p, int64_t rows, int32_t CX, int32_t CY, int32_t mode, tp::Shape &sh) {
     if (!p) return set_error(E3J_B200_INVALID_ARGUMENT, "plan is null");
     if (rows < 0 || CX <= 0 || CY <= 0) return set_error(E3J_B200_INVALID_ARGUMENT, "bad tensor product sizes");
@@ -634,6 +671,25 @@ int e3j_b200_tensor_product(const e3j_b200_tp_plan *p, const float *x, const flo
     if (rc || rows == 0) return rc;
     if (!x || !y || !out) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
     const int grid = (int)std::min<int64_t>(rows, 148 * 16);
+    if (tp_vec4_ok(sh, {x, y, out})) {
+        const size_t smem4 = (tp::table_floats(p->nnz) + tp::kRowsPerBlock * tp::vec4_warp_floats(sh, false)) * sizeof(float);
+        if (smem4 <= kTpStagedSmem) {
+            if (smem4 > 48 * 1024)
+                E3JB_CUDA_TRY(cudaFuncSetAttribute(tp::fwd_vec4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+            const int g4 = (int)std::min<int64_t>(ceil_div64(rows, tp::kRowsPerBlock), 148 * 16);
+            tp::fwd_vec4_kernel<<<g4, dim3(32, tp::kRowsPerBlock), smem4, stream>>>(
+                tp::Table{p->d_val[0], p->d_idx[0], p->nnz}, x, y, out, rows, sh);
+            return check_launch("tensor_product", 0, stream);
+        }
+    }
+    const size_t smem = (tp::table_floats(p->nnz) + (size_t)sh.X * sh.CX + (size_t)sh.Y * sh.CY) * sizeof(float);
+    if (smem <= kTpStagedSmem) {
+        if (smem > 48 * 1024)
+            E3JB_CUDA_TRY(cudaFuncSetAttribute(tp::fwd_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tp::fwd_staged_kernel<<<grid, tp::kThreads, smem, stream>>>(tp::Table{p->d_val[0], p->d_idx[0], p->nnz}, x, y,
+                                                                    out, rows, sh);
+        return check_launch("tensor_product", 0, stream);
+    }
     tp::fwd_kernel<<<grid, tp::kThreads, 0, stream>>>(tp::Table{p->d_val[0], p->d_idx[0], p->nnz}, x, y, out, rows, sh);
     return check_launch("tensor_product", 0, stream);
 }
@@ -646,6 +702,28 @@ int e3j_b200_tensor_product_bwd(const e3j_b200_tp_plan *p, const float *x, const
     if (rc || rows == 0) return rc;
     if (!x || !y || !dz || !dx || !dy) return set_error(E3J_B200_INVALID_ARGUMENT, "null operand");
     const int grid = (int)std::min<int64_t>(rows, 148 * 16);
+    if (tp_vec4_ok(sh, {x, y, dz, dx, dy})) {
+        const size_t smem4 = (2 * tp::table_floats(p->nnz) + tp::kRowsPerBlock * tp::vec4_warp_floats(sh, true)) * sizeof(float);
+        if (smem4 <= 2 * kTpStagedSmem) {
+            if (smem4 > 48 * 1024)
+                E3JB_CUDA_TRY(cudaFuncSetAttribute(tp::bwd_vec4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+            const int g4 = (int)std::min<int64_t>(ceil_div64(rows, tp::kRowsPerBlock), 148 * 16);
+            tp::bwd_vec4_kernel<<<g4, dim3(32, tp::kRowsPerBlock), smem4, stream>>>(
+                tp::Table{p->d_val[1], p->d_idx[1], p->nnz}, tp::Table{p->d_val[2], p->d_idx[2], p->nnz}, x, y, dz, dx, dy,
+                rows, sh);
+            return check_launch("tensor_product_bwd", 0, stream);
+        }
+    }
+    const size_t smem = (2 * tp::table_floats(p->nnz) + (size_t)sh.X * sh.CX + (size_t)sh.Y * sh.CY +
+                         (size_t)sh.Z * sh.CZ + (tp::kThreads / 32) * tp::kMaxY) * sizeof(float);
+    if (smem <= kTpStagedSmem) {
+        if (smem > 48 * 1024)
+            E3JB_CUDA_TRY(cudaFuncSetAttribute(tp::bwd_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        tp::bwd_staged_kernel<<<grid, tp::kThreads, smem, stream>>>(tp::Table{p->d_val[1], p->d_idx[1], p->nnz},
+                                                                    tp::Table{p->d_val[2], p->d_idx[2], p->nnz}, x, y,
+                                                                    dz, dx, dy, rows, sh);
+        return check_launch("tensor_product_bwd", 0, stream);
+    }
     tp::bwd_dx_kernel<<<grid, tp::kThreads, 0, stream>>>(tp::Table{p->d_val[1], p->d_idx[1], p->nnz}, y, dz, dx, rows, sh);
     rc = check_launch("tensor_product_bwd (dx)", 0, stream);
     if (rc) return rc;

@@ -159,5 +159,298 @@ __global__ void __launch_bounds__(kThreads) bwd_dy_kernel(Table by_k, const floa
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same three sums with the row's operands and the table staged in shared memory first
+// (coalesced loads, one barrier), so the table loops read shared memory only.  Used when
+// the row fits; the kernels above remain for larger rows.
+// Dynamic shared memory: table idx (int4) | table val | row operands.
+// ---------------------------------------------------------------------------
+struct SmemTable {
+    const float *val;
+    const int4 *idx;
+    int32_t nnz;
+};
+
+__device__ __forceinline__ SmemTable stage_table(const Table &t, float *&smem) {
+    int4 *sidx = reinterpret_cast<int4 *>(smem);
+    float *sval = reinterpret_cast<float *>(sidx + t.nnz);
+    for (int n = threadIdx.x; n < t.nnz; n += blockDim.x) {
+        sidx[n] = t.idx[n];
+        sval[n] = t.val[n];
+    }
+    smem = sval + ((t.nnz + 3) / 4) * 4;
+    return {sval, sidx, t.nnz};
+}
+
+__device__ __forceinline__ void stage_row(float *dst, const float *src, int count) {
+    for (int q = threadIdx.x; q < count; q += blockDim.x) dst[q] = src[q];
+}
+
+__host__ __device__ inline size_t table_floats(int nnz) { return (size_t)nnz * 4 + (size_t)((nnz + 3) / 4) * 4; }
+
+__global__ void __launch_bounds__(kThreads) fwd_staged_kernel(Table by_i, const float *__restrict__ x,
+                                                              const float *__restrict__ y, float *__restrict__ out,
+                                                              int64_t rows, Shape sh) {
+    extern __shared__ __align__(16) float tp_smem[];
+    float *smem = tp_smem;
+    const SmemTable tab = stage_table(by_i, smem);
+    float *xs = smem, *ys = xs + sh.X * sh.CX;
+    for (int64_t n = blockIdx.x; n < rows; n += gridDim.x) {
+        __syncthreads();  // previous row done with xs / ys (and, first time, the table is complete)
+        stage_row(xs, x + n * sh.X * sh.CX, sh.X * sh.CX);
+        stage_row(ys, y + n * sh.Y * sh.CY, sh.Y * sh.CY);
+        __syncthreads();
+        float *on = out + n * sh.Z * sh.CZ;
+        for (int c = threadIdx.x; c < sh.CZ; c += blockDim.x) {
+            int u, v;
+            channels_of(sh, c, u, v);
+            int t = 0;
+            for (int i = 0; i < sh.Z; i++) {
+                float acc = 0.f;
+                for (; t < tab.nnz && tab.idx[t].x == i; t++) {
+                    const int4 id = tab.idx[t];
+                    acc = fmaf(tab.val[t] * ys[id.z * sh.CY + v], xs[id.y * sh.CX + u], acc);
+                }
+                on[(int64_t)i * sh.CZ + c] = acc;
+            }
+        }
+    }
+}
+
+// dx and dy of one row in one kernel: x, y and dz rows staged once.
+__global__ void __launch_bounds__(kThreads) bwd_staged_kernel(Table by_j, Table by_k, const float *__restrict__ x,
+                                                              const float *__restrict__ y,
+                                                              const float *__restrict__ dz, float *__restrict__ dx,
+                                                              float *__restrict__ dy, int64_t rows, Shape sh) {
+    extern __shared__ __align__(16) float tp_smem[];
+    float *smem = tp_smem;
+    const SmemTable tj = stage_table(by_j, smem);
+    const SmemTable tk = stage_table(by_k, smem);
+    float *xs = smem, *ys = xs + sh.X * sh.CX, *gs = ys + sh.Y * sh.CY, *part = gs + (size_t)sh.Z * sh.CZ;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int64_t n = blockIdx.x; n < rows; n += gridDim.x) {
+        __syncthreads();
+        stage_row(xs, x + n * sh.X * sh.CX, sh.X * sh.CX);
+        stage_row(ys, y + n * sh.Y * sh.CY, sh.Y * sh.CY);
+        stage_row(gs, dz + n * sh.Z * sh.CZ, sh.Z * sh.CZ);
+        __syncthreads();
+        float *dxn = dx + n * sh.X * sh.CX, *dyn = dy + n * sh.Y * sh.CY;
+        for (int u = threadIdx.x; u < sh.CX; u += blockDim.x) {
+            int t = 0;
+            for (int j = 0; j < sh.X; j++) {
+                float acc = 0.f;
+                for (; t < tj.nnz && tj.idx[t].y == j; t++) {
+                    const int4 id = tj.idx[t];
+                    float inner = 0.f;
+                    if (sh.mode == MAP) {
+                        inner = ys[id.z * sh.CY + u] * gs[id.x * sh.CZ + u];
+                    } else {
+                        for (int v = 0; v < sh.CY; v++)
+                            inner = fmaf(ys[id.z * sh.CY + v], gs[id.x * sh.CZ + u * sh.CY + v], inner);
+                    }
+                    acc = fmaf(tj.val[t], inner, acc);
+                }
+                dxn[j * sh.CX + u] = acc;
+            }
+        }
+        if (sh.mode == MAP) {
+            for (int v = threadIdx.x; v < sh.CY; v += blockDim.x) {
+                int t = 0;
+                for (int k = 0; k < sh.Y; k++) {
+                    float acc = 0.f;
+                    for (; t < tk.nnz && tk.idx[t].z == k; t++) {
+                        const int4 id = tk.idx[t];
+                        acc = fmaf(tk.val[t] * xs[id.y * sh.CX + v], gs[id.x * sh.CZ + v], acc);
+                    }
+                    dyn[k * sh.CY + v] = acc;
+                }
+            }
+        } else if (sh.CY == 1) {
+            int t = 0;
+            for (int k = 0; k < sh.Y; k++) {
+                int t1 = t;
+                while (t1 < tk.nnz && tk.idx[t1].z == k) t1++;
+                float acc = 0.f;
+                for (int u = threadIdx.x; u < sh.CX; u += blockDim.x)
+                    for (int q = t; q < t1; q++) {
+                        const int4 id = tk.idx[q];
+                        acc = fmaf(tk.val[q] * xs[id.y * sh.CX + u], gs[id.x * sh.CZ + u], acc);
+                    }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) part[warp * kMaxY + k] = acc;
+                t = t1;
+            }
+            __syncthreads();
+            for (int k = threadIdx.x; k < sh.Y; k += blockDim.x) {
+                float total = 0.f;
+                for (int w = 0; w < nwarp; w++) total += part[w * kMaxY + k];
+                dyn[k] = total;
+            }
+        } else {
+            for (int v = threadIdx.x; v < sh.CY; v += blockDim.x) {
+                int t = 0;
+                for (int k = 0; k < sh.Y; k++) {
+                    float acc = 0.f;
+                    for (; t < tk.nnz && tk.idx[t].z == k; t++) {
+                        const int4 id = tk.idx[t];
+                        float inner = 0.f;
+                        for (int u = 0; u < sh.CX; u++)
+                            inner = fmaf(xs[id.y * sh.CX + u], gs[id.x * sh.CZ + u * sh.CY + v], inner);
+                        acc = fmaf(tk.val[t], inner, acc);
+                    }
+                    dyn[k * sh.CY + v] = acc;
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Four channels per lane, one warp per row (CX a multiple of 4; MAP, or OUTER with CY == 1).
+// The warp stages its row's operands in its own part of shared memory (128-bit loads,
+// __syncwarp only); blockDim = (32, kRowsPerBlock).  Dynamic shared memory:
+// table | per warp: x [X][Q] float4 | g [Z][Q] float4 (backward only) | y.
+// ---------------------------------------------------------------------------
+constexpr int kRowsPerBlock = 4;
+
+__device__ __forceinline__ SmemTable stage_table_block(const Table &t, float *&smem) {
+    int4 *sidx = reinterpret_cast<int4 *>(smem);
+    float *sval = reinterpret_cast<float *>(sidx + t.nnz);
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x, nthr = blockDim.x * blockDim.y;
+    for (int n = tid; n < t.nnz; n += nthr) {
+        sidx[n] = t.idx[n];
+        sval[n] = t.val[n];
+    }
+    smem = sval + ((t.nnz + 3) / 4) * 4;
+    return {sval, sidx, t.nnz};
+}
+
+__device__ __forceinline__ float4 fma4(float a, const float4 &b, const float4 &c) {
+    return make_float4(fmaf(a, b.x, c.x), fmaf(a, b.y, c.y), fmaf(a, b.z, c.z), fmaf(a, b.w, c.w));
+}
+__device__ __forceinline__ float4 mul4(const float4 &a, const float4 &b) {
+    return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+}
+
+// floats one warp needs: x quads, (backward) dz quads, y (padded to whole float4)
+__host__ __device__ inline size_t vec4_warp_floats(const Shape &sh, bool backward) {
+    return (size_t)sh.X * sh.CX + (backward ? (size_t)sh.Z * sh.CZ : 0) + (((size_t)sh.Y * sh.CY + 3) / 4) * 4;
+}
+
+__global__ void __launch_bounds__(32 * kRowsPerBlock) fwd_vec4_kernel(Table by_i, const float *__restrict__ x,
+                                                                      const float *__restrict__ y,
+                                                                      float *__restrict__ out, int64_t rows, Shape sh) {
+    extern __shared__ __align__(16) float tp_smem[];
+    float *smem = tp_smem;
+    const SmemTable tab = stage_table_block(by_i, smem);
+    __syncthreads();
+    const int lane = threadIdx.x, Q = sh.CX / 4, ylen = sh.Y * sh.CY;
+    float *mine = smem + (size_t)threadIdx.y * vec4_warp_floats(sh, false);
+    float4 *xs = reinterpret_cast<float4 *>(mine);
+    float *ys = mine + (size_t)sh.X * sh.CX;
+    const bool map = sh.mode == MAP;
+    for (int64_t n = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; n < rows; n += (int64_t)gridDim.x * blockDim.y) {
+        __syncwarp();
+        const float4 *xn = reinterpret_cast<const float4 *>(x + n * sh.X * sh.CX);
+        for (int q = lane; q < sh.X * Q; q += 32) xs[q] = xn[q];
+        for (int q = lane; q < ylen; q += 32) ys[q] = y[n * ylen + q];
+        __syncwarp();
+        float4 *on = reinterpret_cast<float4 *>(out + n * sh.Z * sh.CZ);
+        for (int q = lane; q < Q; q += 32) {
+            int t = 0;
+            for (int i = 0; i < sh.Z; i++) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (; t < tab.nnz && tab.idx[t].x == i; t++) {
+                    const int4 id = tab.idx[t];
+                    const float4 xv = xs[id.y * Q + q];
+                    if (map) {
+                        const float4 yv = reinterpret_cast<const float4 *>(ys + id.z * sh.CY)[q];
+                        acc = fma4(tab.val[t], mul4(xv, yv), acc);
+                    } else {
+                        acc = fma4(tab.val[t] * ys[id.z], xv, acc);
+                    }
+                }
+                on[(int64_t)i * Q + q] = acc;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32 * kRowsPerBlock) bwd_vec4_kernel(Table by_j, Table by_k, const float *__restrict__ x,
+                                                                      const float *__restrict__ y,
+                                                                      const float *__restrict__ dz, float *__restrict__ dx,
+                                                                      float *__restrict__ dy, int64_t rows, Shape sh) {
+    extern __shared__ __align__(16) float tp_smem[];
+    float *smem = tp_smem;
+    const SmemTable tj = stage_table_block(by_j, smem);
+    const SmemTable tk = stage_table_block(by_k, smem);
+    __syncthreads();
+    const int lane = threadIdx.x, Q = sh.CX / 4, ylen = sh.Y * sh.CY;
+    float *mine = smem + (size_t)threadIdx.y * vec4_warp_floats(sh, true);
+    float4 *xs = reinterpret_cast<float4 *>(mine);
+    float4 *gs = xs + (size_t)sh.X * Q;
+    float *ys = mine + (size_t)sh.X * sh.CX + (size_t)sh.Z * sh.CZ;
+    const bool map = sh.mode == MAP;
+    for (int64_t n = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; n < rows; n += (int64_t)gridDim.x * blockDim.y) {
+        __syncwarp();
+        const float4 *xn = reinterpret_cast<const float4 *>(x + n * sh.X * sh.CX);
+        const float4 *gn = reinterpret_cast<const float4 *>(dz + n * sh.Z * sh.CZ);
+        for (int q = lane; q < sh.X * Q; q += 32) xs[q] = xn[q];
+        for (int q = lane; q < sh.Z * Q; q += 32) gs[q] = gn[q];  // CZ == CX in both supported cases
+        for (int q = lane; q < ylen; q += 32) ys[q] = y[n * ylen + q];
+        __syncwarp();
+        float4 *dxn = reinterpret_cast<float4 *>(dx + n * sh.X * sh.CX);
+        for (int q = lane; q < Q; q += 32) {
+            int t = 0;
+            for (int j = 0; j < sh.X; j++) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (; t < tj.nnz && tj.idx[t].y == j; t++) {
+                    const int4 id = tj.idx[t];
+                    const float4 gv = gs[id.x * Q + q];
+                    if (map) {
+                        const float4 yv = reinterpret_cast<const float4 *>(ys + id.z * sh.CY)[q];
+                        acc = fma4(tj.val[t], mul4(yv, gv), acc);
+                    } else {
+                        acc = fma4(tj.val[t] * ys[id.z], gv, acc);
+                    }
+                }
+                dxn[j * Q + q] = acc;
+            }
+        }
+        if (map) {
+            float4 *dyn = reinterpret_cast<float4 *>(dy + n * sh.Y * sh.CY);
+            for (int q = lane; q < Q; q += 32) {
+                int t = 0;
+                for (int k = 0; k < sh.Y; k++) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (; t < tk.nnz && tk.idx[t].z == k; t++) {
+                        const int4 id = tk.idx[t];
+                        acc = fma4(tk.val[t], mul4(xs[id.y * Q + q], gs[id.x * Q + q]), acc);
+                    }
+                    dyn[k * Q + q] = acc;
+                }
+            }
+        } else {  // CY == 1: sum over every channel, fixed order: lane's quads, its 4 channels, butterfly
+            int t = 0;
+            for (int k = 0; k < sh.Y; k++) {
+                int t1 = t;
+                while (t1 < tk.nnz && tk.idx[t1].z == k) t1++;
+                float acc = 0.f;
+                for (int q = lane; q < Q; q += 32)
+                    for (int r = t; r < t1; r++) {
+                        const int4 id = tk.idx[r];
+                        const float4 p = mul4(xs[id.y * Q + q], gs[id.x * Q + q]);
+                        acc = fmaf(tk.val[r], (p.x + p.y) + (p.z + p.w), acc);
+                    }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) dy[n * sh.Y + k] = acc;
+                t = t1;
+            }
+        }
+    }
+}
+
 }  // namespace tp
 }  // namespace e3jb

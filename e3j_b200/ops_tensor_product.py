@@ -124,3 +124,40 @@ def tensor_product(coef, x: torch.Tensor, y: torch.Tensor, params: CUDATensorPro
 
 
 tensor_product.Params = CUDATensorProductParams
+
+
+class _ScatterAdd1Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, values, indices, num_out):
+        ctx.save_for_backward(indices)
+        lead = values.shape[:-1]
+        rows = int(np.prod(lead)) if len(lead) else 1
+        num_idx = int(values.shape[-1])
+        val = values.reshape(rows, num_idx).contiguous()
+        out = torch.empty((rows, num_out), dtype=torch.float32, device=values.device)
+        need = int(_lib.lib().e3j_b200_scatter_add_1_workspace_bytes(num_idx, num_out))
+        ws = torch.empty(need, dtype=torch.uint8, device=values.device)
+        with torch.cuda.device(values.device):
+            _lib.check(_lib.lib().e3j_b200_scatter_add_1(_ptr(indices), _ptr(val), _ptr(out), rows, num_idx, num_out,
+                                                         _ptr(ws), need, _stream()))  # fmt: skip
+        return out.reshape(*lead, num_out)
+
+    @staticmethod
+    def backward(ctx, ct_out):
+        (indices,) = ctx.saved_tensors
+        idx = indices.to(torch.int64)
+        valid = (idx >= 0) & (idx < ct_out.shape[-1])
+        ct_val = ct_out.index_select(-1, idx.clamp(0, ct_out.shape[-1] - 1)) * valid.to(ct_out.dtype)
+        return ct_val, None, None
+
+
+def scatter_add_1(indices: torch.Tensor, values: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Mirror of ``e3j.ops.scatter_add.scatter_add_1`` (src/e3j/ops/scatter_add.py:27-63):
+    ``(num_idx,) x (..., num_idx) -> (..., num_out)``; ``out`` only gives the result's shape.
+    Sums run in position order (reproducible)."""
+    if values.dtype != torch.float32:
+        raise NotImplementedError("scatter_add_1 computes in float32 here; cast the values.")
+    if indices.ndim != 1 or indices.shape[0] != values.shape[-1]:
+        raise ValueError("expects a 1-D index as long as the last axis of the values")
+    _require_cuda(values.contiguous(), indices.contiguous())
+    return _ScatterAdd1Fn.apply(values, indices.to(torch.int32).contiguous(), int(out.shape[-1]))

@@ -288,6 +288,18 @@ int e3j_b200_tensor_product_bwd(const e3j_b200_tp_plan *plan, const float *x, co
                                 e3j_b200_stream stream);
 
 /*
+ * Scatter-add along the last axis by a 1-D index, the functional counterpart of the reference's
+ * "scatter_add_1" target (lib/e3j_ops/ffi/e3j_ops.h:77-118, src/e3j/ops/scatter_add.py:27-63):
+ *     out[r, o] = sum_{i : idx[i] == o} val[r, i],   val[rows, num_idx], out[rows, num_out].
+ * Written as a gather over the positions grouped (stably) by destination: no atomics, sums in
+ * position order, so results are reproducible; idx need not be sorted; indices outside
+ * [0, num_out) are dropped.  Every element of out is written.
+ */
+size_t e3j_b200_scatter_add_1_workspace_bytes(int64_t num_idx, int32_t num_out);
+int e3j_b200_scatter_add_1(const int32_t *idx, const float *val, float *out, int64_t rows, int64_t num_idx,
+                           int32_t num_out, void *workspace, size_t workspace_bytes, e3j_b200_stream stream);
+
+/*
  * Real harmonics of edge vectors, the producer of `y`, and their vector-Jacobian
  * product (the gradient with respect to positions flows through it).  Replaces the XLA
  * evaluation of e3j.core.Harmonics.__call__ (src/e3j/core/harmonics.py:93-101: optional

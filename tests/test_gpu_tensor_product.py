@@ -69,3 +69,31 @@ def test_unsupported_modes_and_layouts_are_refused():
         tensor_product(coef, x, y, CUDATensorProductParams(1, "OUTER", "LEADING_CHANNELS"))
     with pytest.raises(NotImplementedError):
         tensor_product(coef, x, torch.zeros((2, 1, 3), device=DEV), CUDATensorProductParams(1, "MAP"))
+
+
+@pytest.mark.parametrize("sorted_idx", [True, False])
+def test_scatter_add_1(sorted_idx):
+    """(num_idx,) x (..., num_idx) -> (..., num_out) against numpy's add.at, with indices out of
+    range dropped, empty destinations zero, and the cotangent of the values a gather."""
+    from e3j_b200.ops_tensor_product import scatter_add_1
+
+    rng = np.random.default_rng(4)
+    num_idx, num_out = 1000, 37
+    idx = rng.integers(0, num_out - 2, num_idx)  # destinations 35, 36 stay empty
+    if sorted_idx:
+        idx = np.sort(idx)
+    idx[::97] = num_out + 5  # dropped
+    val = rng.standard_normal((3, 5, num_idx)).astype(np.float32)
+    want = np.zeros((3, 5, num_out))
+    keep = idx < num_out
+    np.add.at(want, (slice(None), slice(None), idx[keep]), val[:, :, keep].astype(np.float64))
+    tv = torch.tensor(val, device=DEV, requires_grad=True)
+    got = scatter_add_1(torch.tensor(idx, device=DEV), tv, torch.empty((3, 5, num_out), device=DEV))
+    assert_close(got.detach().cpu().numpy(), want, what="out")
+    assert not got.detach()[..., num_out - 2 :].any()
+    ct = rng.standard_normal(want.shape).astype(np.float32)
+    got.backward(torch.tensor(ct, device=DEV))
+    want_ct = np.where(keep, ct[..., np.clip(idx, 0, num_out - 1)], 0.0)
+    assert_close(tv.grad.cpu().numpy(), want_ct, what="ct_val")
+    again = scatter_add_1(torch.tensor(idx, device=DEV), tv.detach(), torch.empty((3, 5, num_out), device=DEV))
+    assert torch.equal(again, got.detach())
