@@ -93,6 +93,24 @@ class OracleConvOps:
         dx.copy_(torch.from_numpy(gx)), dy.copy_(torch.from_numpy(gy)), ds.copy_(torch.from_numpy(gs))
 
 
+class SplitOracleConvOps(OracleConvOps):
+    """The oracle behind the pass-by-pass interface of `CudaConvOps` (per-edge pass, then the
+    dx reduction on a range of sender rows), so that the overlapped reverse exchange of
+    `HaloConvolution.backward` runs on CPU ranks too.  NaN marks what a pass must not touch."""
+
+    split_dx = True
+
+    def backward(self, x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, dx, dy, ds, n_recv, n_send,
+                 phases=7, rows=None):
+        full = [torch.empty_like(t) for t in (dx, dy, ds)]
+        super().backward(x, y, s, dm, sender, receiver_ptr, sender_ptr_t, perm_t, *full, n_recv, n_send)
+        if phases & 3:
+            dy.copy_(full[1]), ds.copy_(full[2])
+        if phases & 4:
+            a0, a1 = rows if rows is not None else (0, n_send)
+            dx[a0:a1] = full[0][a0:a1]
+
+
 class TorchRowOps:
     @staticmethod
     def gather(dst, src, idx):
@@ -103,7 +121,7 @@ class TorchRowOps:
         dst[idx] += src
 
 
-def _rank_main(rank, world, port, ret):
+def _rank_main(rank, world, port, ret, split=False):
     import torch.distributed as dist
 
     from e3j_b200.halo import HaloConvolution
@@ -114,14 +132,14 @@ def _rank_main(rank, world, port, ret):
         g, conv, x, y, s, dm, parts = _global_case(world, channels=8)
         p = parts[rank]
         dims = (4, 16, conv.target.dim, conv.num_scalars, 8)
-        halo = HaloConvolution(p, dims, "cpu", OracleConvOps(conv), TorchRowOps)
+        halo = HaloConvolution(p, dims, "cpu", (SplitOracleConvOps if split else OracleConvOps)(conv), TorchRowOps)
         x_loc = torch.full((p.n_loc, 4, 8), float("nan"))
         x_loc[: p.n_own] = torch.from_numpy(x[p.global_ids[: p.n_own]])
         y_l, s_l = torch.from_numpy(y[p.edge_ids]), torch.from_numpy(s[p.edge_ids])
         out = torch.empty((p.n_own, conv.target.dim, 8))
         halo.forward(x_loc, y_l, s_l, out)
         dm_l = torch.from_numpy(dm[p.global_ids[: p.n_own]])
-        dx_loc, dy, ds = torch.empty_like(x_loc), torch.empty_like(y_l), torch.empty_like(s_l)
+        dx_loc, dy, ds = (torch.full_like(t, float("nan")) for t in (x_loc, y_l, s_l))
         halo.backward(x_loc, y_l, s_l, dm_l, dx_loc, dy, ds)
         ret[rank] = dict(ids=p.global_ids[: p.n_own], eids=p.edge_ids, out=out.numpy(), dx=dx_loc[: p.n_own].numpy(),
                          dy=dy.numpy(), ds=ds.numpy(), halo_x=x_loc[p.n_own :].numpy(), halo_ids=p.global_ids[p.n_own :])  # fmt: skip
@@ -135,14 +153,14 @@ def _free_port():
         return sk.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_exchange_protocol_on_cpu_ranks(world):
+@pytest.mark.parametrize("world,split", [(2, False), (3, False), (2, True), (3, True)])
+def test_exchange_protocol_on_cpu_ranks(world, split):
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret, split)) for r in range(world)]
     [p.start() for p in procs]
     [p.join(120) for p in procs]
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
