@@ -126,3 +126,22 @@ def test_slab_partition_owns_every_edge_once_with_consistent_plans(seed, world):
         for q, (a, b) in p.recv_slice.items():  # what arrives from q is what q sends, in the same order
             rows = parts[q].send_rows[p.rank]
             assert (parts[q].global_ids[rows] == p.global_ids[a:b]).all()
+
+
+@settings(**SETTINGS)
+@given(st.integers(0, 10**6), st.sampled_from([("OUTER", 3, 2), ("OUTER", 4, 1), ("MAP", 5, 5)]))
+def test_tensor_product_oracle_backward_is_the_adjoint(seed, shape):
+    from oracle import numpy_oracle
+
+    mode, cx, cy = shape
+    rng = np.random.default_rng(seed)
+    nx, ny, nz, rows = (int(v) for v in rng.integers(1, 6, 4))
+    nnz = int(rng.integers(1, 20))
+    val = rng.standard_normal(nnz).astype(np.float32)
+    idx = np.stack([rng.integers(0, nz, nnz), rng.integers(0, nx, nnz), rng.integers(0, ny, nnz)], axis=-1)
+    x, y = rng.standard_normal((rows, nx, cx)), rng.standard_normal((rows, ny, cy))
+    out = numpy_oracle.tensor_product(val, idx, x, y, nz, mode)
+    dz = rng.standard_normal(out.shape)
+    dx, dy = numpy_oracle.tensor_product_vjp(val, idx, x, y, dz, mode)
+    lhs = (dz * out).sum()
+    assert abs(lhs - (dx * x).sum()) <= 1e-9 * (1 + abs(lhs)) and abs(lhs - (dy * y).sum()) <= 1e-9 * (1 + abs(lhs))
