@@ -196,13 +196,13 @@ def emit_fwd_group(em, vname, gi, group, dims, uform=False):
     em.end()
     em.block("static __device__ __forceinline__ void prefetch(const FwdArgs &A, int64_t e, int32_t a, float4 *stage, float *ysm, int lane)")
     em("a = in_range(a, A.NS) ? a : 0;")
-    em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
-    em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
+    em(f"const float *sp = A.s + (e * {S}) * kC + lane * 4;")
+    em(f"const float *xp = A.x + ((int64_t)a * {X}) * kC + lane * 4;")
     em("float4 *dst = stage + lane;")
     for p in srows:
-        em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * 128);")
+        em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * kC);")
     for j in xrows:
-        em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
+        em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * kC);")
     em(f"if (lane < 4) cp_async16_stream(ysm + lane * 4, A.y + e * {Y} + lane * 4);")
     em.end()
     em.block("static __device__ __forceinline__ void compute(const FwdArgs &A, Acc &c, const float4 *sg, const float *ysm)")
@@ -241,11 +241,11 @@ def emit_fwd_group(em, vname, gi, group, dims, uform=False):
     em.end()  # compute
     em.block("static __device__ __forceinline__ void store(const Acc &c, float4 *o)")
     for z in zs:
-        em(f"o[{z} * 32] = as_float4(c.a{z});")
+        em(f"o[{z} * kC4] = as_float4(c.a{z});")
     em.end()
     em.block("static __device__ __forceinline__ void store_zero(float4 *o, const float4 &zero4)")
     for z in zs:
-        em(f"o[{z} * 32] = zero4;")
+        em(f"o[{z} * kC4] = zero4;")
     em.end()
     em.end("};")
     em()
@@ -298,23 +298,23 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
         em(f"static constexpr int kGBase = {g_base}, kGRows = {len(zrows)};  // rows of the staged dm block it reads")
         em.block("static __device__ __forceinline__ void prefetch(const BwdArgs &A, int64_t e, int32_t a, float4 *slot, int lane)")
         em("a = in_range(a, A.NS) ? a : 0;")
-        em(f"const float *sp = A.s + (e * {S}) * 128 + lane * 4;")
-        em(f"const float *xp = A.x + ((int64_t)a * {X}) * 128 + lane * 4;")
+        em(f"const float *sp = A.s + (e * {S}) * kC + lane * 4;")
+        em(f"const float *xp = A.x + ((int64_t)a * {X}) * kC + lane * 4;")
         em("float4 *dst = slot + lane;")
         for p in srows:
-            em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * 128);")
+            em(f"cp_async16_stream(dst + {slot_s[p]} * 32, sp + {p} * kC);")
         for j in xrows:
-            em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * 128);")
+            em(f"cp_async16_keep(dst + {slot_x[j]} * 32, xp + {j} * kC);")
         em.end()
         em.block("static __device__ __forceinline__ void compute(const BwdArgs &A, const float4 *sg, const float4 *gsm, const float *ysm, int64_t e, bool valid, int lane, DyAcc (&dyp)[16])")
-        em(f"float4 *ds_out = reinterpret_cast<float4 *>(A.ds + (e * {S}) * 128) + lane;")
-        em(f"float4 *dx_out = reinterpret_cast<float4 *>(A.dxm + (e * {X}) * 128) + lane;")
+        em(f"float4 *ds_out = reinterpret_cast<float4 *>(A.ds + (e * {S}) * kC) + lane;")
+        em(f"float4 *dx_out = reinterpret_cast<float4 *>(A.dxm + (e * {X}) * kC) + lane;")
         em("const f4 zero4 = zero_f4();")
         em.block("if (!valid)")
         for p in srows:
-            em(f"st_stream4(ds_out + {p} * 32, zero4);")
+            em(f"st_stream4(ds_out + {p} * kC4, zero4);")
         for j in xrows:
-            em(f"st_stream4(dx_out + {j} * 32, zero4);")
+            em(f"st_stream4(dx_out + {j} * kC4, zero4);")
         em("return;")
         em.end()
         em("const float4 *ysm4 = reinterpret_cast<const float4 *>(ysm);")
@@ -342,12 +342,12 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
                 em(f"{{ f4 dsv = mul_vv(x{js[0]}, v{js[0]});")
                 for j in js[1:]:
                     em(f"  fma_vv(dsv, x{j}, v{j});")
-                em(f"  st_stream4(ds_out + {path.p} * 32, dsv); }}")
+                em(f"  st_stream4(ds_out + {path.p} * kC4, dsv); }}")
                 for j in js:
                     em(f"fma_vv(dx{j}, sv, v{j});")
                 em.end()
             for j in grp[0].xrows:
-                em(f"st_stream4(dx_out + {j} * 32, dx{j});")
+                em(f"st_stream4(dx_out + {j} * kC4, dx{j});")
             em.end()
         em.end()
         em.end("};")
@@ -358,14 +358,20 @@ def emit_bwd(em, vname, paths, dims, slot_rows):
     return chunks
 
 
-def emit_variant(em, v):
+CHANNELS = (128, 256)  # tensors' channel counts; a kernel always works on one block of 128 channels of them
+
+
+def emit_variant(em, v, channels=128):
     vid, name, x_irreps, nw = v["id"], v["name"], v["x"], v["nw"]
+    if channels != 128:
+        vid, name = vid + 10 * (channels // 128 - 1), f"{name}_c{channels}"
     conv, idx, paths = analyse(x_irreps)
     X, Y, Z, S = conv.source[0].dim, conv.source[1].dim, conv.target.dim, conv.num_scalars
     nnz = len(idx)
     em(f"// ===== variant {vid} ({name}): x = {x_irreps}, y = {Y_IRREPS}, filter {OUT_FILTER} =====")
     em(f"namespace {name} {{")
     em(f"static constexpr int kId = {vid}, X = {X}, Y = {Y}, Z = {Z}, S = {S}, NNZ = {nnz};")
+    em(f"static constexpr int kC = {channels}, kC4 = kC / 4;  // row length of the tensors in floats / float4 (a launch covers 128 channels)")
     em(f"static constexpr int NW = {nw}, RPC = {v['rpc']}, NST = {v['nst']}, kFwdMinCtas = {v['fmin']}, kFwdRotate = {v['rot']}, kFwdSplit = {v['fsplit']}, kFwdCtaWarps = {v['fw'] if v['fsplit'] else v['nw'] * v['rpc']};")
     em(f"static constexpr int kBwdWarps = {v['bw']}, kBwdSlots = {v['nslot']}, kBwdSlotRows = {v['slot_rows']}, kBwdMinCtas = {v['bmin']}, kBwdSplit = {v['bsplit']}, kBwdGBuf = {v.get('gbuf', 1)};")
     em(f"static const uint8_t pattern[NNZ][4] = {{{', '.join('{%d,%d,%d,%d}' % tuple(r) for r in idx)}}};")
@@ -411,7 +417,7 @@ def emit_variant(em, v):
     em("#include \"conv_unrolled_entry.inc\"")
     em(f"}}  // namespace {name}")
     em()
-    return dict(id=vid, name=name, X=X, Y=Y, Z=Z, S=S, nnz=nnz, groups=[[p.p for p in g] for g in groups],
+    return dict(id=vid, name=name, C=channels, X=X, Y=Y, Z=Z, S=S, nnz=nnz, groups=[[p.p for p in g] for g in groups],
                 group_cost=[sum(p.cost_fwd for p in g) for g in groups], fwd_rows=rows, chunks=len(chunks))
 
 
@@ -424,7 +430,7 @@ def main():
     em = Emitter()
     em("// GENERATED by gen_unrolled.py — do not edit; regenerate instead.")
     em("// clang-format off")
-    infos = [emit_variant(em, v) for v in VARIANTS]
+    infos = [emit_variant(em, v, c) for c in CHANNELS for v in VARIANTS]
     out = os.environ.get("E3J_B200_GEN_OUT") or os.path.join(HERE, "conv_unrolled_gen.inc")
     with open(out, "w") as fh:
         fh.write(em.text())

@@ -378,3 +378,26 @@ def test_more_unrolled_variants(x_irreps, variant, nodes):
     assert gplan.variant == 0
     for a, b, name in ((out, gout, "out"), (dx, gdx, "dx"), (dy, gdy, "dy"), (ds, gds, "ds")):
         assert_close(a, b, what=name + " vs table-driven")
+
+
+@pytest.mark.parametrize("cfg,variant,nodes", [(0, 11, 300), (2, 12, 150)])
+def test_unrolled_variants_with_256_channels(cfg, variant, nodes):
+    """C = 256 runs the unrolled kernels as two blocks of 128 channels (dy summed over both)."""
+    conv = Convolution((problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER, graph_ordering="RECEIVER", avg_num_neighbors=20.0)
+    g = problems.make_graph(cfg, seed=5, num_nodes=nodes)
+    inp = problems.make_inputs(g, cfg, conv.num_scalars, conv.source[0].dim, channels=256, seed=5)
+    val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
+    rng = np.random.default_rng(1)
+    dm = rng.standard_normal((g.num_nodes, conv.target.dim, 256)).astype(np.float32)
+    (out, dx, dy, ds), plan = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, conv.target.dim, dm,
+                                      idx_dtype="uint8", poison=True)  # fmt: skip
+    assert plan.variant == variant
+    ptr = csr_ptr(g.receiver, g.num_nodes)
+    ptr_t, perm_t = c_oracle.transpose_csr(g.sender, g.num_nodes)
+    assert_close(out, c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, g.sender, ptr, conv.target.dim), what="out")
+    wdx, wdy, wds = c_oracle.conv_bwd(val, idx4, inp.x, inp.y, inp.s, dm, g.sender, ptr, ptr_t, perm_t)
+    assert_close(dx, wdx, what="dx")
+    assert_close(dy, wdy, what="dy")
+    assert_close(ds, wds, what="ds")
+    (out2, dx2, dy2, ds2), _ = run_raw(val, idx4, inp.x, inp.y, inp.s, g.sender, g.receiver, conv.target.dim, dm, idx_dtype="uint8")
+    assert np.array_equal(out, out2) and np.array_equal(dx, dx2) and np.array_equal(dy, dy2) and np.array_equal(ds, ds2)
