@@ -214,8 +214,8 @@ def run_ours(args):
     conv = Convolution((args.x_irreps or problems.X_IRREPS[cfg], problems.Y_IRREPS), problems.OUT_FILTER,
                        graph_ordering=args.ordering, avg_num_neighbors=30.0)  # fmt: skip
     g = problems.make_graph(cfg, seed=rank, num_nodes=args.nodes)
-    x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, 128, rank)
-    X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, 128
+    x, y, s, _, _ = problems.make_inputs_device(g, cfg, conv.num_scalars, conv.source[0].dim, device, args.channels, rank)
+    X, Y, Z, S, C = conv.source[0].dim, 16, conv.target.dim, conv.num_scalars, args.channels
     plan = ops.get_plan(conv._coef_packed, (X, Y, Z, S, C), device, args.table_driven)
     snd_h, rcv_h = g.sender, g.receiver
     if by_sender:
@@ -386,7 +386,7 @@ def run_ours(args):
     achieved = alg[dominant] / (per_kernel[dominant] * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath) and not by_sender and not args.x_irreps:
+    if os.path.exists(tpath) and not by_sender and not args.x_irreps and C == 128:
         with open(tpath) as fh:
             traffic = json.load(fh).get(f"config{cfg}", {}).get(dominant)
     cpu = time_cpu(cfg, steps=10, warmup=1) if world == 1 and not args.no_cpu else None
@@ -790,6 +790,7 @@ def main():
                     help="tensor_product: time the standalone product (not the headline metric)")
     ap.add_argument("--table-driven", action="store_true",
                     help="N = 1: bypass the unrolled kernels (the path of tables that match no variant)")
+    ap.add_argument("--channels", type=int, default=128, help="N = 1: channel count (the configurations use 128)")
     ap.add_argument("--x-irreps", default=None,
                     help="N = 1: node-feature irreps instead of the configuration's (e.g. 0e, 0e+1o+2e), same graph")
     ap.add_argument("--ordering", default="RECEIVER", choices=["RECEIVER", "SENDER"],
