@@ -384,14 +384,33 @@ __global__ void bwd_finish_kernel(const int32_t *__restrict__ receiver_ptr, int3
 // backward, pass 2: dx[a] = sum over the sender segment of the edges' dx messages,
 // in sender-sorted order.  One block per sender row; rows of XC floats.
 // ---------------------------------------------------------------------------
+// Optional extra duty of the dx reduction: zero dy and ds of the edges at or beyond
+// receiver_ptr[N] (what bwd_finish_kernel does when there are no partial dy buffers to sum),
+// which saves that launch.  receiver_ptr == nullptr: nothing to do.
+struct TailZero {
+    const int32_t *receiver_ptr;
+    int32_t N;
+    int64_t E;
+    float *dy;
+    int64_t dy_row;
+    float *ds;
+    int64_t ds_row;
+};
+
 template <int VEC>
 __global__ void __launch_bounds__(256) dx_reduce_kernel(const float *__restrict__ dxm,
                                                         const int32_t *__restrict__ sender_ptr_t,
                                                         const int32_t *__restrict__ perm_t,
                                                         float *__restrict__ dx, int32_t N,
-                                                        int64_t XC) {
+                                                        int64_t XC, TailZero tail) {
     using V = typename std::conditional<VEC == 4, float4, float>::type;
     const int64_t nvec = XC / VEC;
+    if (tail.receiver_ptr) {
+        const int64_t first = max((int64_t)0, min((int64_t)tail.receiver_ptr[tail.N], tail.E));
+        const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+        for (int64_t t = first * tail.dy_row + tid; t < tail.E * tail.dy_row; t += step) tail.dy[t] = 0.f;
+        for (int64_t t = first * tail.ds_row + tid; t < tail.E * tail.ds_row; t += step) tail.ds[t] = 0.f;
+    }
     for (int64_t a = blockIdx.x; a < N; a += gridDim.x) {
         const int32_t p0 = sender_ptr_t[a], p1 = sender_ptr_t[a + 1];
         for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {

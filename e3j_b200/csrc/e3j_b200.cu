@@ -173,7 +173,8 @@ int e3j_b200_plan_launches(const e3j_b200_plan *p, int32_t *fwd, int32_t *bwd) {
     if (!p || !fwd || !bwd) return set_error(E3J_B200_INVALID_ARGUMENT, "plan_launches: null argument");
     const bool un = p->variant != E3J_B200_VARIANT_GENERIC;
     *fwd = un ? p->un.fwd_launches : 1;
-    *bwd = (un ? p->un.dy_partials : 1) + 2;  // per-edge pass(es) + dy finish + dx reduction
+    const int parts = un ? p->un.dy_partials : 1;
+    *bwd = parts + (parts > 1 ? 2 : 1);  // per-edge pass(es) + dx reduction, + the finish pass when it sums dy buffers
     return E3J_B200_OK;
 }
 
@@ -439,7 +440,11 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
             if (rc) return rc;
         }
     }
-    if (E > 0 && (phases & E3J_B200_BWD_TAIL)) {
+    // With a single dy buffer the finish pass only zeroes the tail; the dx reduction takes that over
+    // when it runs in the same call on the whole graph (one launch less per step).
+    const bool tail_in_dx = E > 0 && (phases & E3J_B200_BWD_TAIL) && (phases & E3J_B200_BWD_DX) && nparts == 1 &&
+                            !window && !edge_perm && NS > 0;
+    if (E > 0 && (phases & E3J_B200_BWD_TAIL) && !tail_in_dx) {
         generic::bwd_finish_kernel<<<p->lim.sm_count * 8, 256, 0, stream>>>(
             receiver_ptr, N, e0, E, edge_perm, dxm, (int64_t)d.X * d.C, dy, d.Y, ds, (int64_t)d.S * d.C, dy_part, nparts);
         rc = check_launch("convolution_bwd (tail)", debug, stream);
@@ -457,10 +462,11 @@ static int bwd_core(const e3j_b200_plan *p, const float *x, const float *y, cons
     const int grid = (int)std::min<int64_t>(NS, (int64_t)p->lim.sm_count * 16);
     const bool vec4 = XC % 4 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
     const int threads = (int)std::min<int64_t>(256, std::max<int64_t>(32, (XC / (vec4 ? 4 : 1) + 31) / 32 * 32));
+    const generic::TailZero tail{tail_in_dx ? receiver_ptr : nullptr, N, E, dy, d.Y, ds, (int64_t)d.S * d.C};
     if (vec4)
-        generic::dx_reduce_kernel<4><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
+        generic::dx_reduce_kernel<4><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC, tail);
     else
-        generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC);
+        generic::dx_reduce_kernel<1><<<grid, threads, 0, stream>>>(dxm, sender_ptr_t, perm_t, dx, NS, XC, tail);
     return check_launch("convolution_bwd (dx)", debug, stream);
 }
 
