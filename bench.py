@@ -93,6 +93,9 @@ def cpu_sample(config: int, seed: int, target_edges: int):
 
 
 def time_cpu(config: int, steps: int, warmup: int, seed: int = 0, target_edges: int | None = None):
+    # All host cores for the CPU arm: torchrun exports OMP_NUM_THREADS=1 to its workers, which would
+    # time the baseline on one core.  Set before the OpenMP runtime of the oracle library starts.
+    os.environ["OMP_NUM_THREADS"] = os.environ.get("E3J_B200_CPU_THREADS", str(len(os.sched_getaffinity(0))))
     from oracle import c_oracle
 
     target_edges = target_edges or CPU_SAMPLE_EDGES[config]
@@ -102,8 +105,7 @@ def time_cpu(config: int, steps: int, warmup: int, seed: int = 0, target_edges: 
     ptr[: rows + 1] = ptr_rows
     val, idx4 = conv.coef.val, conv.coef.idx.astype(np.int32)
     ptr_t, perm_t = c_oracle.transpose_csr(sub.sender, n)
-    cores = len(os.sched_getaffinity(0))
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    cores = int(os.environ["OMP_NUM_THREADS"])
 
     def step():
         out = c_oracle.conv_fwd(val, idx4, inp.x, inp.y, inp.s, sub.sender, ptr, conv.target.dim, wide=False)
